@@ -101,6 +101,30 @@ void xalm_cuda_host_free(void* p);
 int xalm_cuda_finalize(xalm_cuda_model* m);
 void xalm_cuda_destroy(xalm_cuda_model* m);
 
+/* ---- model families described by a config.json -------------------------------------------------------------------------
+ * The handle-based calls of this header serve every model family; a handle knows its family.  Llama/Mistral checkpoints
+ * (.xalm) are created with xalm_cuda_create above.  A model folder with a config.json ("architecture": "<name>") and a
+ * model.safetensors is created here: the backend parses the JSON text itself and picks the family registered under that
+ * name (XALM_ERR_UNSUPPORTED when this build carries none).  Then, as for every family: xalm_cuda_upload_tensor once per
+ * tensor (names as in the safetensors header; XALM_BF16 / XALM_F16 / XALM_F32 payloads), xalm_cuda_finalize,
+ * xalm_cuda_prefill / xalm_cuda_forward for the running sequence, xalm_cuda_release when it ends.
+ *   max_tokens: the most positions a sequence may hold (sizes the cache; windowed layers keep a ring of their window only).
+ *   precision:  XALM_PRECISION_BF16 = the serving mode (16-bit matrix operands and K/V cache, fp32 accumulation, fp32 for
+ *               norms, scores, softmax, recurrent state and the residual stream);
+ *               XALM_PRECISION_F32  = everything in IEEE fp32 (no TF32), the K/V cache included. */
+enum xalm_precision { XALM_PRECISION_BF16 = 0, XALM_PRECISION_F32 = 1 };
+int xalm_cuda_create_json(const char* config_json, int device, int max_tokens, int precision, xalm_cuda_model** out);
+/* Model families linked into this build ("Llama", "Nabalix", ...). */
+int xalm_cuda_family_count(void);
+const char* xalm_cuda_family_name(int index);
+/* The sequence is over: what it holds in the K/V cache and the recurrent state is given back; the next call starts at
+ * position 0.  (Llama handles: a no-op, their ring is overwritten by position.) */
+int xalm_cuda_release(xalm_cuda_model* m);
+/* For loaders: tensor `index` the model expects (name, element shape of `*rank` <= 4 dims); XALM_ERR_INVALID past the last. */
+int xalm_cuda_expected_tensor(xalm_cuda_model* m, int index, char* name, size_t name_cap, int* shape4, int* rank);
+/* Integer properties by name: "vocab_size", "dim", "n_layers", "max_tokens", "position" (tokens the sequence holds). */
+int xalm_cuda_model_info(xalm_cuda_model* m, const char* key, long long* value);
+
 /* Tensor parallel plumbing (no reference analogue; north star).  Rank 0 makes an id, the host side ships it to
  * the other ranks (torch.distributed / MPI / a file), every rank calls comm_init before finalize. */
 #define XALM_COMM_ID_BYTES 128

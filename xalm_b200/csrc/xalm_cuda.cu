@@ -10,6 +10,8 @@
 //              matvec[norm -> W1|W3 -> GLU] hb = act(W1 xb) * (W3 xb)
 //              matvec[W2, residual]         x += W2 hb                     (TP: partial -> allreduce -> add)
 //   matvec[norm -> classifier]              logits                         (skipped in HYDRATE_KV_CACHE mode)
+#include "llama_names.h"
+
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <math.h>
@@ -31,67 +33,11 @@
 #include "matvec_mma.cuh"
 #include "decode_mega.h"
 #include "prefill.h"
+#include "family.h"
 
 namespace xalm {
 
-thread_local std::string g_last_error;
-
-int set_error(int status, const char* fmt, ...) {
-	char buf[1024];
-	va_list ap;
-	va_start(ap, fmt);
-	vsnprintf(buf, sizeof buf, fmt, ap);
-	va_end(ap);
-	g_last_error = buf;
-	return status;
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// tuning knobs (xalm_cuda_tune): integers looked up by name, so GPU sweeps need no recompilation
-// ---------------------------------------------------------------------------------------------------------
-static std::map<std::string, int>& tuning() {
-	static std::map<std::string, int> t = {
-	    {"pdl", 1},          // programmatic dependent launch between the kernels of a token
-	    {"graph", 1},        // replay a captured CUDA graph per token
-	    {"attn_splits", 0},  // 0 = auto (~1 CTA per SM, at most 32 splits per kv head)
-	    {"attn_min_split", 128},
-	    {"mv_cfg_rows", 0},  // 0 = auto, 1 = force config A (R4 KS1 NW4), 2 = force config B (R2 KS4 NW8)
-	    {"mega", 0},         // EXPERIMENTAL, measured slower than the kernel-per-op path (profiles/r2_token_kernel.md): one persistent kernel per
-	                         // token (decode_mega.cu) when the model allows — single GPU, integer weight formats
-	    {"mega_smem_kb", 170}, // shared memory per CTA the token kernel may take: the ring gets what the staged activations leave (3 stages on a
-	                           // 7B model: deeper rings measured no faster), the rest of the 228 KB stays L1
-	    {"mega_ns_max", 16},
-	    {"mega_quiet", 1},   // the token kernel's producer pauses while the consumers hand over between phases
-	    {"mega_coop", 1},    // cooperative launch of the token kernel
-	    {"mega_timeline", 0}, // record per-phase %globaltimer stamps (xalm_cuda_mega_timeline)
-	    {"tma", 1},          // stream weights with cp.async.bulk into a shared-memory ring (matvec_tma.cuh)
-	    {"idp", 1},          // integer weight formats: integer-dot consumers (matvec_idp.cuh) instead of the float ones
-	    {"tma_smem_kb", 100}, // shared-memory budget per CTA for the TMA kernel (two kernels co-reside under PDL)
-	    {"tma_rc_small", 8}, // rows per tile when the matrix has few rows (Wo, W2)
-	    {"tma_xstage_max_kb", 32}, // rows longer than this (in fp32 bytes) are not staged in smem when there is no norm
-	    {"tma_norm_kw4", 0}, {"tma_norm_smem_kb", 72},
-	    {"tma_rc", 0},       // 0 = auto, else force rows per tile (4 or 8)
-	    {"tma_ns_max", 4},   // most ring stages
-	    {"tma_ctas_per_sm", 2},
-	    {"tma_short_rows", 1}, // rows of <= 64 pieces without a norm prologue: 16-row tiles with 1-2 K-slices (all lanes busy)
-	    {"tma_grid_even", 0}, // percent: shrink the persistent grid down to this fraction of the full one if that makes tiles % grid == 0
-	    {"tp_fused", 1},     // tensor parallel: fuse the two per-layer exchanges into the matvec kernels (push over NVLink + receive in the next prologue)
-	    {"idp_per_sm", 2},
-	    {"mma", 2},         // integer formats on the tensor-core matvec (fragment tiles + mma.sync int8, matvec_mma.cuh): 0 = never (unit layout + dp4a), 1 = all six, 2 = the 4/5-bit formats, and the 8-bit ones under tensor parallelism (measured on one GPU: q4_0 1.68 vs 1.86 ms/token; q8_0 1.90 vs 1.86)
-    {"idp_ng", 0},      // consumer groups per CTA of the integer-dot matvec: 0 = by format, 2 = one 17-warp CTA per SM, 1 = two 9-warp CTAs
-	    {"tail_prefetch_mb", 8}, // each decode kernel pulls this many MB of the NEXT kernel's first weights into L2 once its own loads are issued
-	    {"prefill_split", 3}, // batched prefill operand precision: 1 = fp16 x fp16 (fastest; logits drift ~4e-2 over 32 layers), 2 = hi+lo fp16
-	                          // activations, 3 = hi+lo on activations, weights and attention operands (default: logits within ~1e-3 of the decode path)
-	};
-	return t;
-}
-static int tune(const char* k) {
-	const char* e = nullptr;
-	std::string env = std::string("XALM_") + k;
-	for (auto& ch : env) ch = (char) toupper(ch);
-	if ((e = getenv(env.c_str()))) return atoi(e);
-	return tuning()[k];
-}
+// g_last_error / set_error / tune(): abi.cu
 
 // ---------------------------------------------------------------------------------------------------------
 // launch helper (optionally with the programmatic-stream-serialisation attribute = PDL)
@@ -873,6 +819,7 @@ struct LayerDev {
 enum { P_ATT_NORM = 0, P_FFN_NORM, P_Q, P_K, P_V, P_O, P_GATE, P_DOWN, P_UP };
 
 struct xalm_cuda_model {
+	xalm::ModelHead head = {nullptr}; // first member: which family the handle belongs to (family.h)
 	xalm_config c;
 	int device = 0, tp_rank = 0, tp_size = 1;
 	// local (per-rank) sizes
@@ -954,26 +901,11 @@ static int parse_tensor_name(const char* name, int n_layers, int* layer, int* pi
 
 extern "C" {
 
-int xalm_cuda_abi_version(void) { return XALM_CUDA_ABI_VERSION; }
-const char* xalm_cuda_last_error(void) { return g_last_error.c_str(); }
-
-int xalm_cuda_device_count(int* count) {
-	if (!count) return set_error(XALM_ERR_INVALID, "count is NULL");
-	XALM_CUDA_CHECK(cudaGetDeviceCount(count));
-	return XALM_OK;
-}
-
 int xalm_cuda_type_info(int type_id, int* block_elems, int* block_bytes) {
 	TypeInfo ti;
 	if (!type_info(type_id, &ti)) return set_error(XALM_ERR_INVALID, "invalid type: %d", type_id);
 	if (block_elems) *block_elems = ti.block;
 	if (block_bytes) *block_bytes = ti.bytes;
-	return XALM_OK;
-}
-
-int xalm_cuda_tune(const char* key, int value) {
-	if (!key || !tuning().count(key)) return set_error(XALM_ERR_INVALID, "unknown tuning key '%s'", key ? key : "(null)");
-	tuning()[key] = value;
 	return XALM_OK;
 }
 
@@ -1000,6 +932,7 @@ int xalm_cuda_create(const xalm_config* cfg, int device, int tp_rank, int tp_siz
 	if (device < 0 || device >= ndev) return set_error(XALM_ERR_CUDA, "device %d not available (%d devices)", device, ndev);
 	XALM_CUDA_CHECK(cudaSetDevice(device));
 	xalm_cuda_model* m = new xalm_cuda_model();
+	m->head.family = xalm::find_family("Llama");
 	m->c = c;
 	m->device = device; m->tp_rank = tp_rank; m->tp_size = tp_size;
 	m->q_dim = c.n_heads * c.head_dim;
@@ -1146,16 +1079,6 @@ static int expected_shape(const xalm_cuda_model* m, int piece, int* er, int* ec,
 		default: return set_error(XALM_ERR_INVALID, "unknown tensor");
 	}
 	return XALM_OK;
-}
-
-void* xalm_cuda_host_alloc(size_t nbytes) {
-	void* p = nullptr;
-	cudaError_t e = cudaMallocHost(&p, nbytes ? nbytes : 16);
-	if (e != cudaSuccess) { set_error(XALM_ERR_CUDA, "cudaMallocHost(%zu) failed: %s", nbytes, cudaGetErrorString(e)); return nullptr; }
-	return p;
-}
-void xalm_cuda_host_free(void* p) {
-	if (p) cudaFreeHost(p);
 }
 
 int xalm_cuda_shard_range(xalm_cuda_model* m, const char* name, int* range4) {
@@ -2179,3 +2102,22 @@ int xalm_cuda_bench_matvec(int type_id, int n, int d, int epi, int with_norm, in
 }
 
 } // extern "C"
+
+// ---- the Llama/Mistral family's row of the model registry (family.h) ------------------------------------------------------
+static int llama_release(xalm_cuda_model*) { return XALM_OK; } // the ring is addressed by position: a new sequence overwrites it
+static int llama_info(xalm_cuda_model* m, const char* key, long long* value) {
+	if (!m || !key || !value) return xalm::set_error(XALM_ERR_INVALID, "NULL argument");
+	const std::string k = key;
+	if (k == "vocab_size") *value = m->c.vocab_size;
+	else if (k == "dim") *value = m->c.dim;
+	else if (k == "n_layers") *value = m->c.n_layers;
+	else if (k == "max_tokens") *value = m->c.max_seq_len;
+	else return xalm::set_error(XALM_ERR_INVALID, "unknown property '%s'", key);
+	return XALM_OK;
+}
+static const xalm::ModelFamily llama_family = {
+    "Llama", nullptr, xalm_cuda_upload_tensor, xalm_cuda_shard_range, xalm_cuda_upload_tensor_shard, xalm_cuda_finalize, xalm_cuda_destroy,
+    xalm_cuda_comm_init, xalm_cuda_ipc_export, xalm_cuda_ipc_import, xalm_cuda_set_stream, xalm_cuda_forward, xalm_cuda_forward_argmax,
+    xalm_cuda_forward_async, xalm_cuda_sync, xalm_cuda_prefill, xalm_cuda_prefill_async, xalm_cuda_logits_host, xalm_cuda_active_bytes,
+    xalm_cuda_last_launch_count, xalm_cuda_read_state, xalm_cuda_read_kv, xalm_cuda_mega_timeline, llama_release, nullptr, llama_info, xalm_cuda_create};
+static const xalm::FamilyRegistrar llama_registrar(&llama_family);
