@@ -80,7 +80,14 @@ SYMBOLS = {
     "xalm_cuda_prefill_async": (_i, [_vp, _vp, _i, _i, _i]),
     "xalm_cuda_gemm": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i]),
     "xalm_cuda_bench_gemm": (_i, [_i, _i, _i, _i, _i, _fp]),
+    "xalm_cuda_create_json": (_i, [C.c_char_p, _i, _i, _i, C.POINTER(_vp)]),
+    "xalm_cuda_family_count": (_i, []),
+    "xalm_cuda_family_name": (C.c_char_p, [_i]),
+    "xalm_cuda_release": (_i, [_vp]),
+    "xalm_cuda_expected_tensor": (_i, [_vp, _i, C.c_char_p, _sz, C.POINTER(_i), C.POINTER(_i)]),
+    "xalm_cuda_model_info": (_i, [_vp, C.c_char_p, C.POINTER(C.c_longlong)]),
 }
+PRECISION_BF16, PRECISION_F32 = 0, 1            # enum xalm_precision
 
 _LIB = None
 
@@ -118,6 +125,12 @@ def device_count() -> int:
     n = C.c_int(0)
     check(lib().xalm_cuda_device_count(C.byref(n)))
     return n.value
+
+
+def families() -> list:
+    """Model families linked into the library ("Llama", "Nabalix", ...)."""
+    L = lib()
+    return [L.xalm_cuda_family_name(i).decode() for i in range(L.xalm_cuda_family_count())]
 
 
 def tune(key: str, value: int):

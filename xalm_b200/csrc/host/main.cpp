@@ -1,6 +1,11 @@
 // main.cpp — the reference's CLI surface (src/main.cpp:417-547) on top of the CUDA backend.
 //
 //   xalm_main <checkpoint.xalm> [-d cuda] [-m completion|passkey|perplexity] [-T ctx] [-i prompt | -f file] [-n steps] [-l pos]
+//   xalm_main <model folder>    [-m completion|perplexity|trace] [-T max tokens] [-p bf16|f32] [-i "id id ..."] [-n steps] [-o dir]
+//
+// A model folder (config.json + model.safetensors) is served by the family its "architecture" names; it carries no tokenizer,
+// so prompts are token ids.  `-m trace` replays steps read from standard input through the same step function (Model::prefill_all
+// / Model::release) and writes the logits asked for to `-o`.
 //
 // Same flags, same prefix matching for -m/-d, same defaults (mode completion, -n 128, the default prompt), same stats
 // block, plus the roofline fraction.  Differences, on purpose:
@@ -19,6 +24,7 @@
 #include <sstream>
 #include <string>
 
+#include "json.h"
 #include "model.h"
 
 namespace {
@@ -34,6 +40,11 @@ namespace {
 	fprintf(stderr, "\nPerplexity mode options:\n  Choose one:\n    -i <string> input prompt\n    -f <filepath> input file with prompt\n");
 	fprintf(stderr, "Completion mode options:\n  -n <int>    number of steps to run for in completion mode, default 128. 0 = max_seq_len, -1 = infinite\n");
 	fprintf(stderr, "  Choose one:\n    -i <string> input prompt\n    -f <filepath> input file with prompt\n");
+	fprintf(stderr, "Model folders (config.json + model.safetensors): prompts are token ids (-i \"5 17 3\");\n");
+	fprintf(stderr, "  -p [bf16,f32] precision (default - bf16)   -T <int> most tokens a sequence holds (default 4096)\n");
+	fprintf(stderr, "  -m trace -o <dir>  replay steps from standard input, one JSON object a line:\n");
+	fprintf(stderr, "     {\"step\": 0, \"entries\": [{\"id\": \"a\", \"tokens\": [5, 17, 3], \"want\": [0, 2]}], \"end\": []}\n");
+	fprintf(stderr, "     writes <dir>/<step>.f32 (logits at the wanted places) and prints 'done <step>' after every step\n");
 	fprintf(stderr, "Passkey mode options:\n  -n <int>    number of junk lines to insert (default - 250)\n  -l <int>    passkey position (-1 - random)\n");
 	exit(1);
 }
@@ -219,6 +230,133 @@ int run_verify(const std::string& checkpoint_path, const std::string& convert_ty
 	return 0;
 }
 
+// ---- model folders ------------------------------------------------------------------------------------------------------
+std::vector<int> parse_ids(const std::string& text) {
+	std::vector<int> ids;
+	std::istringstream in(text);
+	std::string w;
+	while (in >> w) {
+		size_t used = 0;
+		const int v = std::stoi(w, &used);
+		if (used != w.size() || v < 0) throw std::invalid_argument("a model folder has no tokenizer: the prompt is a list of token ids, got '" + w + "'");
+		ids.push_back(v);
+	}
+	if (ids.empty()) throw std::invalid_argument("empty prompt");
+	return ids;
+}
+
+// run_completion for a model folder: prompt ids in one batched pass, then greedy steps
+void run_completion_dir(const std::string& path, const std::string& prompt, int max_tokens, int precision, int num_steps) {
+	const ModelDir dir = ModelDir::load(path);
+	std::cout << "loading model " << path << " (" << dir.arch << ")" << std::endl;
+	Model model = Model::from_dir(dir, max_tokens, precision);
+	model.cuda();
+	InferenceState state(model.config);
+	state.cuda();
+	Sampler sampler(model.config);
+	std::vector<int> encoding = parse_ids(prompt);
+	if (num_steps <= 0) num_steps = model.config.max_seq_len - (int) encoding.size();
+	num_steps = std::min(num_steps, model.config.max_seq_len - (int) encoding.size());
+	const double t0 = now_s();
+	size_t read_bytes = model.active_bytes(encoding.size() - 1);
+	if (!model.prefill(state, encoding.data(), (int) encoding.size(), 0, InferenceMode::OUTPUT_LOGITS)) throw std::runtime_error("the prompt does not fit max tokens");
+	const double hydrate_s = now_s() - t0;
+	for (int i = 0; i < num_steps; i++) {
+		const int token_id = sampler.sample_argmax(state);
+		std::cout << token_id << " " << std::flush;
+		encoding.push_back(token_id);
+		if (i + 1 == num_steps) break;
+		model.forward(state, token_id, (int) encoding.size() - 1);
+		read_bytes += model.active_bytes(encoding.size() - 1);
+	}
+	std::cout << "\n" << std::endl;
+	model.release();
+	const double elapsed_s = now_s() - t0;
+	const double gbs = (double) read_bytes / 1e9 / elapsed_s;
+	printf("Generation stats:\n  %zu tokens\n  throughput: %.5gtok/s\n  latency: %.5gs/tok\n  hydrate: %.5gs\n  bandwidth: %.5gGB/s\n  total: %.5gs\n",
+	       encoding.size(), encoding.size() / elapsed_s, elapsed_s / encoding.size(), hydrate_s, gbs, elapsed_s);
+}
+
+void run_perplexity_dir(const std::string& path, const std::string& prompt, int max_tokens, int precision) {
+	const ModelDir dir = ModelDir::load(path);
+	Model model = Model::from_dir(dir, max_tokens, precision);
+	model.cuda();
+	InferenceState state(model.config);
+	state.cuda();
+	const std::vector<int> encoding = parse_ids(prompt);
+	if (encoding.size() < 2) throw std::invalid_argument("perplexity needs at least two tokens");
+	const size_t N = encoding.size() - 1;
+	std::vector<float> probs(N);
+	const double t0 = now_s();
+	if (!model.prefill(state, encoding.data(), (int) N, 0, InferenceMode::OUTPUT_LOGITS, encoding.data() + 1, probs.data()))
+		throw std::runtime_error("the input does not fit max tokens");
+	double sum_logprob = 0.0, ss_logprob = 0.0;
+	for (size_t i = 0; i < N; i++) {
+		const double lp = std::log(probs[i]);
+		sum_logprob += lp;
+		ss_logprob += lp * lp;
+	}
+	const double elapsed_s = now_s() - t0, perplexity = std::exp(-sum_logprob / N);
+	printf("Stats:\n  %zu tokens\n  perplexity: %.5g ± %.5g\n  throughput: %.5gtok/s\n  total: %.5gs\n", N, perplexity,
+	       perplexity * std::sqrt(std::max(0.0, ss_logprob - sum_logprob * sum_logprob / N) / N / N), N / elapsed_s, elapsed_s);
+}
+
+// -m trace: one request at a time (this engine holds one sequence), each step the request's next tokens
+int run_trace(const std::string& path, int max_tokens, int precision, const std::string& out_dir) {
+	if (out_dir.empty()) { fprintf(stderr, "Error: -m trace needs -o <dir>\n"); return 1; }
+	const ModelDir dir = ModelDir::load(path);
+	Model model = Model::from_dir(dir, max_tokens, precision);
+	model.cuda();
+	const size_t V = (size_t) model.config.vocab_size;
+	std::string live; // the request whose tokens the cache and state hold
+	int pos = 0;
+	std::vector<float> logits, picked;
+	std::vector<int> tokens;
+	std::string line;
+	while (std::getline(std::cin, line)) {
+		if (line.find_first_not_of(" \t\r\n") == std::string::npos) continue;
+		const xjson::Value st = xjson::Parser::parse(line.data(), line.size());
+		const long long step = st.at("step").inum;
+		picked.clear();
+		for (const xjson::Value& e : st.at("entries").arr) {
+			const std::string id = e.at("id").str;
+			if (id != live) {
+				if (!live.empty()) throw std::runtime_error("request '" + id + "' starts while '" + live + "' is live: this engine holds one sequence");
+				live = id;
+				pos = 0;
+			}
+			tokens.clear();
+			for (const xjson::Value& t : e.at("tokens").arr) tokens.push_back((int) t.inum);
+			const auto& want = e.at("want").arr;
+			if (tokens.empty()) continue;
+			const int n = (int) tokens.size();
+			if (!want.empty()) logits.resize((size_t) n * V);
+			model.prefill_all(tokens.data(), n, pos, want.empty() ? nullptr : logits.data());
+			pos += n;
+			for (const xjson::Value& w : want) {
+				if (w.inum < 0 || w.inum >= n) throw std::invalid_argument("want: place outside the step's tokens");
+				picked.insert(picked.end(), logits.begin() + (size_t) w.inum * V, logits.begin() + (size_t) (w.inum + 1) * V);
+			}
+		}
+		if (const xjson::Value* end = st.find("end"))
+			for (const xjson::Value& e : end->arr)
+				if (e.str == live) {
+					model.release();
+					live.clear();
+					pos = 0;
+				}
+		if (!picked.empty()) {
+			const std::string fn = out_dir + "/" + std::to_string(step) + ".f32";
+			FILE* f = fopen(fn.c_str(), "wb");
+			if (!f || fwrite(picked.data(), 4, picked.size(), f) != picked.size()) throw std::runtime_error("cannot write " + fn);
+			fclose(f);
+		}
+		printf("done %lld\n", step);
+		fflush(stdout);
+	}
+	return 0;
+}
+
 bool is_prefix_of(const std::string& full, const std::string& s) { return !s.empty() && full.compare(0, s.size(), s) == 0; }
 
 } // namespace
@@ -227,7 +365,8 @@ int main(int argc, char* argv[]) {
 	std::string checkpoint_path, device = "cuda", mode = "completion";
 	std::string prompt = "Q: What is the meaning of life? A:"; // main.cpp:421
 	std::string prompt_path;
-	std::string convert_type;
+	std::string convert_type, out_dir;
+	int precision = XALM_PRECISION_BF16;
 	int context = 0, num_steps = 128, n_junk = 250, passkey_pos = -1;
 	if (argc >= 2) checkpoint_path = argv[1];
 	else error_usage();
@@ -240,6 +379,7 @@ int main(int argc, char* argv[]) {
 			else if (is_prefix_of("passkey", v)) mode = "passkey";
 			else if (is_prefix_of("perplexity", v)) mode = "perplexity";
 			else if (is_prefix_of("verify", v)) mode = "verify";
+			else if (is_prefix_of("trace", v)) mode = "trace";
 			else error_usage();
 		} else if (f == 'd') {
 			if (is_prefix_of("cpu", v)) device = "cpu";
@@ -249,6 +389,12 @@ int main(int argc, char* argv[]) {
 		else if (f == 'f') prompt_path = v;
 		else if (f == 'T') context = std::stoi(v);
 		else if (f == 't') convert_type = v;
+		else if (f == 'o') out_dir = v;
+		else if (f == 'p') {
+			if (v == "bf16" || v == "bfloat16") precision = XALM_PRECISION_BF16;
+			else if (v == "f32" || v == "float32") precision = XALM_PRECISION_F32;
+			else error_usage();
+		}
 		else if (f == 'l') passkey_pos = std::stoi(v);
 		else if (f == 'n') { num_steps = std::stoi(v); n_junk = num_steps; }
 		else error_usage();
@@ -266,6 +412,26 @@ int main(int argc, char* argv[]) {
 		fprintf(stderr, "Error: this binary is the CUDA backend; it carries no CPU forward pass (use the reference for -d cpu)\n");
 		return 1;
 	}
+	if (ModelDir::is_model_dir(checkpoint_path)) {
+		try {
+			if (mode == "trace") return run_trace(checkpoint_path, context, precision, out_dir);
+			if (!prompt_path.empty()) {
+				std::ifstream file(prompt_path);
+				if (!file.is_open()) { std::cerr << "Error: could not open file " << prompt_path << std::endl; return 1; }
+				std::stringstream buffer;
+				buffer << file.rdbuf();
+				prompt = buffer.str();
+			}
+			if (mode == "completion") run_completion_dir(checkpoint_path, prompt, context, precision, num_steps);
+			else if (mode == "perplexity") run_perplexity_dir(checkpoint_path, prompt, context, precision);
+			else { fprintf(stderr, "Error: mode %s needs a tokenizer; a model folder has none\n", mode.c_str()); return 1; }
+		} catch (const std::exception& e) {
+			fprintf(stderr, "error: %s\n", e.what());
+			return 1;
+		}
+		return 0;
+	}
+	if (mode == "trace") { fprintf(stderr, "Error: -m trace takes a model folder\n"); return 1; }
 	if (mode == "completion" || mode == "perplexity") {
 		if (!prompt_path.empty()) { // the reference's default prompt makes `-f` alone an error (main.cpp:513-517); -f simply wins here
 			std::ifstream file(prompt_path);

@@ -269,8 +269,91 @@ xalm_config Config::to_c() const {
 InferenceState::InferenceState(const Config& config) : own_logits_((size_t) config.vocab_size, 0.f) {}
 
 // ---- Model -------------------------------------------------------------------------------------------------------
-Model::Model(Model&& o) noexcept : config(o.config), device(o.device), host_(std::move(o.host_)), types_(std::move(o.types_)), handle_(o.handle_), tp_size_(o.tp_size_) {
+Model::Model(Model&& o) noexcept : config(o.config), device(o.device), host_(std::move(o.host_)), types_(std::move(o.types_)), deferred_(o.deferred_),
+                                   dir_(o.dir_), max_tokens_(o.max_tokens_), precision_(o.precision_), handle_(o.handle_), tp_size_(o.tp_size_) {
 	o.handle_ = nullptr;
+}
+
+// ---- ModelDir ----------------------------------------------------------------------------------------------------
+bool ModelDir::is_model_dir(const std::string& path) {
+	std::error_code ec;
+	return std::filesystem::is_directory(path, ec) && std::filesystem::exists(std::filesystem::path(path) / "config.json", ec);
+}
+
+ModelDir ModelDir::load(const std::string& dir) {
+	ModelDir d;
+	d.dir = dir;
+	{
+		std::ifstream f(dir + "/config.json", std::ios::binary);
+		if (!f) throw std::runtime_error("cannot open " + dir + "/config.json");
+		d.config_json.assign(std::istreambuf_iterator<char>(f), std::istreambuf_iterator<char>());
+	}
+	const xjson::Value cfg = xjson::Parser::parse(d.config_json.data(), d.config_json.size());
+	if (const xjson::Value* a = cfg.find("architecture"); a && a->kind == xjson::Value::String) d.arch = a->str;
+	else throw std::invalid_argument(dir + "/config.json names no architecture");
+	const std::string st = dir + "/model.safetensors";
+	std::ifstream f(st, std::ios::binary);
+	if (!f) throw std::runtime_error("cannot open " + st);
+	uint64_t hlen = 0;
+	f.read(reinterpret_cast<char*>(&hlen), 8);
+	if (!f || hlen == 0 || hlen > (1ull << 31)) throw std::invalid_argument(st + ": bad header length");
+	std::string hj((size_t) hlen, '\0');
+	f.read(hj.data(), (std::streamsize) hlen);
+	if (!f) throw std::invalid_argument(st + ": truncated header");
+	f.seekg(0, std::ios::end);
+	const size_t file_size = (size_t) f.tellg();
+	const xjson::Value h = xjson::Parser::parse(hj.data(), hj.size());
+	for (const auto& [name, v] : h.obj) {
+		if (name == "__metadata__") continue;
+		tensor_info ti;
+		ti.name = name;
+		const std::string dt = v.at("dtype").str;
+		size_t esz = 0;
+		if (dt == "F32") { ti.type = Type::from_id(XALM_F32); esz = 4; }
+		else if (dt == "F16") { ti.type = Type::from_id(XALM_F16); esz = 2; }
+		else if (dt == "BF16") { ti.type = Type::from_id(XALM_BF16); esz = 2; }
+		else if (dt == "I32" || dt == "U32") esz = 4;
+		else if (dt == "I64" || dt == "U64") esz = 8;
+		else if (dt == "U8" || dt == "I8") esz = 1;
+		else throw std::invalid_argument(st + ": tensor " + name + " has dtype " + dt);
+		size_t count = 1;
+		for (const auto& dsz : v.at("shape").arr) { ti.shape.push_back((int) dsz.inum); count *= (size_t) dsz.inum; }
+		const auto& off = v.at("data_offsets").arr;
+		if (off.size() != 2) throw std::invalid_argument(st + ": tensor " + name + ": data_offsets");
+		ti.offset = 8 + (size_t) hlen + (size_t) off[0].unum;
+		ti.size = (size_t) (off[1].unum - off[0].unum);
+		if (ti.size != count * esz || ti.offset + ti.size > file_size) throw std::invalid_argument(st + ": tensor " + name + ": size does not fit its shape");
+		d.tensors.emplace(name, std::move(ti));
+	}
+	return d;
+}
+
+void ModelDir::read(const tensor_info& ti, uint8_t* dst) const {
+	const std::string st = dir + "/model.safetensors";
+	const int fd = ::open(st.c_str(), O_RDONLY);
+	if (fd < 0) throw std::runtime_error("cannot open " + st);
+	size_t done = 0;
+	while (done < ti.size) {
+		const ssize_t r = ::pread(fd, dst + done, ti.size - done, (off_t) (ti.offset + done));
+		if (r <= 0) { ::close(fd); throw std::runtime_error(st + ": read failed for " + ti.name); }
+		done += (size_t) r;
+	}
+	::close(fd);
+}
+
+Model Model::from_dir(const ModelDir& dir, const int max_tokens, const int precision) {
+	Config c{};
+	c.max_seq_len = max_tokens > 0 ? max_tokens : 4096;
+	Model m(c);
+	m.dir_ = &dir;
+	m.max_tokens_ = c.max_seq_len;
+	m.precision_ = precision;
+	return m;
+}
+
+void Model::release() const {
+	if (!handle_) throw std::runtime_error("Model::release: model is not on a CUDA device");
+	if (xalm_cuda_release(handle_) != XALM_OK) xalm_throw_last("model.release()");
 }
 Model::~Model() {
 	if (handle_) xalm_cuda_destroy(handle_);
@@ -317,6 +400,33 @@ Model Model::from_xalm(Xalm::file_info& xalm, const int context, const bool defe
 
 void Model::cuda(int device_index, int tp_rank, int tp_size, const void* comm_id) {
 	if (handle_) return;
+	if (dir_) { // a config.json family: the backend says which tensors it reads
+		if (tp_size != 1) throw std::invalid_argument("model.cuda(): config.json families run on one GPU");
+		if (xalm_cuda_create_json(dir_->config_json.c_str(), device_index, max_tokens_, precision_, &handle_) != XALM_OK) xalm_throw_last("model.cuda()");
+		size_t cap = 16;
+		for (const auto& [name, ti] : dir_->tensors) cap = std::max(cap, ti.size);
+		uint8_t* stage = static_cast<uint8_t*>(xalm_cuda_host_alloc(cap));
+		if (!stage) xalm_throw_last("model.cuda()");
+		struct Guard { uint8_t* p; ~Guard() { xalm_cuda_host_free(p); } } guard{stage};
+		char name[256];
+		int shape[4], rank = 0;
+		for (int i = 0; xalm_cuda_expected_tensor(handle_, i, name, sizeof name, shape, &rank) == XALM_OK; i++) {
+			const auto it = dir_->tensors.find(name);
+			if (it == dir_->tensors.end()) continue; // optional tensors may be absent; finalize names a missing required one
+			const ModelDir::tensor_info& ti = it->second;
+			if (ti.type.id == XALM_UNKNOWN) throw std::invalid_argument(std::string("tensor ") + name + " is an integer table");
+			dir_->read(ti, stage);
+			if (xalm_cuda_upload_tensor(handle_, name, ti.type.id, ti.shape.data(), (int) ti.shape.size(), stage, ti.size) != XALM_OK)
+				xalm_throw_last("model.cuda()");
+		}
+		if (xalm_cuda_finalize(handle_) != XALM_OK) xalm_throw_last("model.cuda()");
+		long long v = 0;
+		if (xalm_cuda_model_info(handle_, "vocab_size", &v) == XALM_OK) config.vocab_size = (int) v;
+		if (xalm_cuda_model_info(handle_, "dim", &v) == XALM_OK) config.dim = (int) v;
+		if (xalm_cuda_model_info(handle_, "n_layers", &v) == XALM_OK) config.n_layers = (int) v;
+		device = Device::CUDA;
+		return;
+	}
 	const xalm_config c = config.to_c();
 	if (xalm_cuda_create(&c, device_index, tp_rank, tp_size, &handle_) != XALM_OK) xalm_throw_last("model.cuda()");
 	tp_size_ = tp_size;
@@ -366,6 +476,11 @@ void Model::cuda(int device_index, int tp_rank, int tp_size, const void* comm_id
 }
 
 size_t Model::active_bytes(const size_t pos) const {
+	if (dir_) { // config.json families count their own bytes (weights once, visible cache rows, recurrent state)
+		long long b = 0;
+		if (!handle_ || xalm_cuda_active_bytes(handle_, (long long) pos, &b) != XALM_OK) return 0;
+		return (size_t) b;
+	}
 	// model.cpp:12-35 in 64-bit with per-format bytes (the reference's int arithmetic overflows at 128256 x 4096 x 16)
 	auto wb = [&](const std::string& name, size_t elems) { return types_.at(name).nbytes(elems); };
 	const size_t dim = config.dim, hidden = config.hidden_dim, q_dim = (size_t) config.n_heads * config.head_dim,
@@ -412,6 +527,11 @@ bool Model::prefill(const InferenceState& s, const int* tokens, const int n, con
 		std::abort();
 	}
 	return true;
+}
+
+void Model::prefill_all(const int* tokens, const int n, const int pos0, float* all_logits) const {
+	if (device != Device::CUDA || !handle_) throw std::runtime_error("Model::prefill_all: model is not on a CUDA device");
+	if (xalm_cuda_prefill(handle_, tokens, n, pos0, all_logits ? 2 : 0, all_logits, nullptr, nullptr) != XALM_OK) xalm_throw_last("model.prefill_all()");
 }
 
 // ---- Sampler (sampler.cpp:3-30) ----------------------------------------------------------------------------------

@@ -101,6 +101,23 @@ struct Xalm {
 	static unsigned long long xxh3(const void* p, size_t n); // XXH3_64bits (0 when the library is missing)
 };
 
+// ---- model folders described by a config.json: <dir>/config.json + <dir>/model.safetensors ------------------------------
+// (no reference analogue: the reference reads .xalm only).  A safetensors file is an 8-byte little-endian header length,
+// that many bytes of JSON (name -> dtype, shape, data_offsets from the end of the header) and the payloads.
+struct ModelDir {
+	struct tensor_info {
+		std::string name;
+		Type type;               // F32 / F16 / BF16; XALM_UNKNOWN for integer tables (never uploaded)
+		std::vector<int> shape;
+		size_t offset = 0, size = 0; // absolute
+	};
+	std::string dir, config_json, arch;
+	std::map<std::string, tensor_info> tensors;
+	static ModelDir load(const std::string& dir);
+	static bool is_model_dir(const std::string& path); // a directory that holds a config.json
+	void read(const tensor_info& ti, uint8_t* dst) const;
+};
+
 // ---- Config (model.h:25-91) -------------------------------------------------------------------------------------
 enum class ActivationType { GELU, SILU };
 enum class LayerNormType { RMSNorm };
@@ -142,6 +159,14 @@ struct Model {
 	// buffer -> device, and a tensor-parallel rank reads only the rows it keeps (the reference reads everything whole first,
 	// model.cpp:48-118).  The file_info must outlive the cuda() call.
 	static Model from_xalm(Xalm::file_info& xalm, int context, bool defer_load = false);
+	// A model folder: the backend picks the family registered under the config's "architecture" (xalm_cuda_create_json) and
+	// parses the JSON itself; cuda() streams the tensors the family asks for (xalm_cuda_expected_tensor) file -> pinned ->
+	// device.  max_tokens sizes the cache (0: 4096); precision is XALM_PRECISION_BF16 (serving) or XALM_PRECISION_F32.
+	// Of `config` only dim, n_layers, vocab_size and max_seq_len (= max_tokens) are meaningful, and only after cuda().
+	static Model from_dir(const ModelDir& dir, int max_tokens, int precision = XALM_PRECISION_BF16);
+	// The running sequence is over: its cache slots and recurrent state are given back; the next call starts at position 0.
+	void release() const;
+	[[nodiscard]] bool is_json_family() const { return dir_ != nullptr; }
 	Model(Model&&) noexcept;
 	Model(const Model&) = delete;
 	Model& operator=(const Model&) = delete;
@@ -161,11 +186,17 @@ struct Model {
 	bool prefill(const InferenceState& s, const int* tokens, int n, int pos0, InferenceMode mode = InferenceMode::OUTPUT_LOGITS,
 	             const int* targets = nullptr, float* probs = nullptr) const;
 
+	// The same pass with the logits of EVERY position: `all_logits` receives n x vocab_size floats (a step of a replayed trace,
+	// scoring).  Throws where prefill() would return false.
+	void prefill_all(const int* tokens, int n, int pos0, float* all_logits) const;
+
 private:
 	explicit Model(const Config& c) : config(c) {}
 	std::map<std::string, Tensor> host_; // until cuda()
 	std::map<std::string, Type> types_;  // kept for active_bytes after the host copies are gone
 	const Xalm::file_info* deferred_ = nullptr; // defer_load: where cuda() reads the tensors from
+	const ModelDir* dir_ = nullptr;             // from_dir: the folder cuda() reads (must outlive the call)
+	int max_tokens_ = 0, precision_ = 0;
 	xalm_cuda_model* handle_ = nullptr;
 	int tp_size_ = 1;
 };

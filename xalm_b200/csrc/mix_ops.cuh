@@ -1,0 +1,536 @@
+// mix_ops.cuh — sequence-mixing and layer-plumbing mechanisms for model families described by a config.json, each a kernel
+// of its own with its constants as arguments so that another design can use it:
+//
+//   embed_streams_kernel   token rows -> S copies of the residual stream (hyper-connections; S = 1: the plain stream)
+//   hc_norm_kernel         u = sum_s a[s] x_s, then RMS norm with a plain or one-plus weight (the read side of a hyper-connection
+//                          fused with the pre-norm; S = 1, a = {1}: a plain pre-norm)
+//   rows_gemm_kernel       out(T,N) = A(T,K) . W(N,K)^T in IEEE fp32 (weights bf16 or fp32), T > 4
+//   rows_matvec_kernel     the same for T <= 4 (one-token steps): a warp per pair of output columns, 128-bit weight loads
+//     both with the fused epilogues of RowsEpi: plain store; split store that sends the key / value columns of an input projection
+//     straight into the ring cache; clamped GLU on interleaved gate|up columns; hyper-connection write (all streams updated from
+//     the old ones, with the layer scale)
+//   swa_attn_kernel        softmax attention over a sliding window with grouped K/V heads, tanh soft-capping, a logarithmic
+//                          distance bias per head, a head-mixing matrix applied to the scores before the softmax and a sigmoid
+//                          output gate; keys split over CTAs for one-token steps (swa_merge_kernel joins the parts)
+//   hgrn2_kernel           gated linear recurrence S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t with a lower-bounded
+//                          forget gate, state in fp32 carried in device memory, per-head RMS norm of o fused
+//   dual_norm_hc_kernel    y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb) -> layer scale -> hyper-connection write
+//
+// Numerics: everything here is fp32 (expf / tanhf / log1pf, no fast-math); 16-bit storage appears only as weight and K/V-cache
+// element types.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace xalm {
+namespace mix {
+
+constexpr int MAX_STREAMS = 8;
+
+// ---- element access ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float ldf(const float* p) { return *p; }
+__device__ __forceinline__ float ldf(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ void stf(float* p, float v) { *p = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+// eight consecutive elements (16-byte aligned for bf16, 32-byte for fp32) -> fp32
+__device__ __forceinline__ void ld8(const float* p, float* o) {
+	const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+	o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float* o) {
+	const uint4 r = *reinterpret_cast<const uint4*>(p);
+	o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
+	o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
+	o[4] = __uint_as_float(r.z << 16); o[5] = __uint_as_float(r.z & 0xffff0000u);
+	o[6] = __uint_as_float(r.w << 16); o[7] = __uint_as_float(r.w & 0xffff0000u);
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// block-wide sum; every thread gets the result.  `red` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+	v = warp_sum(v);
+	const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+	__syncthreads();
+	if (lane == 0) red[w] = v;
+	__syncthreads();
+	if (w == 0) {
+		float t = lane < nw ? red[lane] : 0.f;
+		t = warp_sum(t);
+		if (lane == 0) red[32] = t;
+	}
+	__syncthreads();
+	return red[32];
+}
+
+// what the kernels of one step read from device memory, so that a captured graph serves every position
+struct SeqStep {
+	int pos0; // position of the step's first token in its sequence
+	int n;    // tokens in the step
+};
+
+// ---- embedding -> streams -------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void embed_streams_kernel(const WT* __restrict__ table, const int* __restrict__ tokens, int width, int S, size_t stream_stride,
+                                     float* __restrict__ xs) {
+	const int t = blockIdx.x;
+	const WT* row = table + (size_t) tokens[t] * width;
+	for (int c = threadIdx.x; c < width; c += blockDim.x) {
+		const float v = ldf(row + c);
+		for (int s = 0; s < S; s++) xs[(size_t) s * stream_stride + (size_t) t * width + c] = v;
+	}
+}
+
+// ---- hyper-connection read + RMS norm -------------------------------------------------------------------------------------
+// h[t] = rmsnorm(sum_s a[s] xs[s][t]) * (one_plus ? 1 + w : w).  a == nullptr: every coefficient is 1 (the final sum of streams).
+// `sum_out` (optional) receives the un-normed combination (the residual stream as a reader outside the model sees it).
+__global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t stream_stride, const float* __restrict__ a, const float* __restrict__ w,
+                               int one_plus, float eps, int width, float* __restrict__ h, float* __restrict__ sum_out) {
+	extern __shared__ float sm[];
+	float* u = sm;            // width
+	float* red = sm + width;  // 33
+	const int t = blockIdx.x;
+	float ss = 0.f;
+	for (int c = threadIdx.x; c < width; c += blockDim.x) {
+		float v = 0.f;
+		for (int s = 0; s < S; s++) {
+			const float x = xs[(size_t) s * stream_stride + (size_t) t * width + c];
+			v = a ? fmaf(a[s], x, v) : v + x;
+		}
+		u[c] = v;
+		ss = fmaf(v, v, ss);
+	}
+	const float tot = block_sum(ss, red);
+	const float r = 1.f / sqrtf(tot / (float) width + eps);
+	for (int c = threadIdx.x; c < width; c += blockDim.x) {
+		const float v = u[c];
+		if (h) h[(size_t) t * width + c] = v * r * (one_plus ? 1.f + w[c] : w[c]);
+		if (sum_out) sum_out[(size_t) t * width + c] = v;
+	}
+}
+
+// ---- fused epilogues of the row products -------------------------------------------------------------------------------------
+enum { EPI_STORE = 0, EPI_SPLIT_KV = 1, EPI_GLU = 2, EPI_HC = 3 };
+struct RowsEpi {
+	int kind = EPI_STORE;
+	float* out = nullptr; // STORE / SPLIT_KV: (T, ldo); GLU: (T, ldo) with ldo = N / 2
+	int ldo = 0;
+	// SPLIT_KV: columns [n_plain, n_plain + kdim) are the step's keys, the next vdim its values; they go to ring slot (pos0 + row) % ring
+	int n_plain = 0, kdim = 0, vdim = 0, ring = 1, cache_f32 = 0;
+	void* kc = nullptr;
+	void* vc = nullptr;
+	const SeqStep* step = nullptr;
+	// GLU: even column = gate, odd = up: y = min(g, limit) * sigmoid(alpha * .) * (clamp(u, +-limit) + 1)
+	float limit = 0.f, alpha = 1.702f;
+	// HC: xs[t'][row][col] = sum_s hmix[s * S + t'] xs[s][row][col] + hout[t'] * scale[col] * value   (hmix / hout NULL: identity / ones)
+	float* xs = nullptr;
+	int S = 1;
+	size_t stream_stride = 0;
+	const float* hmix = nullptr;
+	const float* hout = nullptr;
+	const float* scale = nullptr; // layer scale (NULL: none)
+};
+
+__device__ __forceinline__ float glu_clamped(float g, float u, float limit, float alpha) {
+	g = fminf(g, limit);
+	u = fminf(fmaxf(u, -limit), limit);
+	return g * sigmoidf_(alpha * g) * (u + 1.f);
+}
+
+__device__ __forceinline__ void hc_write(const RowsEpi& e, int row, int col, int width, float v) {
+	const float y = e.scale ? e.scale[col] * v : v;
+	float old[MAX_STREAMS];
+	const size_t at = (size_t) row * width + col;
+	for (int s = 0; s < e.S; s++) old[s] = e.xs[(size_t) s * e.stream_stride + at];
+	for (int t = 0; t < e.S; t++) {
+		float acc;
+		if (e.hmix) {
+			acc = 0.f;
+			for (int s = 0; s < e.S; s++) acc = fmaf(e.hmix[s * e.S + t], old[s], acc);
+		} else acc = old[t];
+		e.xs[(size_t) t * e.stream_stride + at] = fmaf(e.hout ? e.hout[t] : 1.f, y, acc);
+	}
+}
+
+// one value (for the pairwise GLU: called with the even column and both values)
+__device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, int N, float v, float v_next) {
+	switch (e.kind) {
+		case EPI_STORE: e.out[(size_t) row * e.ldo + col] = v; break;
+		case EPI_SPLIT_KV: {
+			if (col < e.n_plain) { e.out[(size_t) row * e.ldo + col] = v; break; }
+			const int slot = (e.step->pos0 + row) % e.ring;
+			const int ck = col - e.n_plain;
+			if (ck < e.kdim) {
+				if (e.cache_f32) ((float*) e.kc)[(size_t) slot * e.kdim + ck] = v;
+				else ((__nv_bfloat16*) e.kc)[(size_t) slot * e.kdim + ck] = __float2bfloat16_rn(v);
+			} else {
+				const int cv = ck - e.kdim;
+				if (e.cache_f32) ((float*) e.vc)[(size_t) slot * e.vdim + cv] = v;
+				else ((__nv_bfloat16*) e.vc)[(size_t) slot * e.vdim + cv] = __float2bfloat16_rn(v);
+			}
+			break;
+		}
+		case EPI_GLU: e.out[(size_t) row * e.ldo + (col >> 1)] = glu_clamped(v, v_next, e.limit, e.alpha); break;
+		case EPI_HC: hc_write(e, row, col, N, v); break;
+	}
+}
+
+// ---- out(T,N) = A(T,K) . W(N,K)^T, fp32 FMA, 64x64x16 tiles, 4x4 per thread ---------------------------------------------------
+template <typename WT>
+__global__ void __launch_bounds__(256) rows_gemm_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
+	constexpr int BM = 64, BN = 64, BK = 16;
+	__shared__ float As[BK][BM + 4];
+	__shared__ float Ws[BK][BN + 4];
+	const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+	const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+	float acc[4][4] = {};
+	for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+		for (int i = 0; i < 4; i++) {
+			const int idx = tid + i * 256; // 0..1023: r = idx / 16, k = idx % 16 (k fastest: coalesced along K)
+			const int r = idx >> 4, k = idx & 15;
+			const int gm = m0 + r, gn = n0 + r, gk = k0 + k;
+			As[k][r] = (gm < T && gk < K) ? A[(size_t) gm * lda + gk] : 0.f;
+			Ws[k][r] = (gn < N && gk < K) ? ldf(W + (size_t) gn * K + gk) : 0.f;
+		}
+		__syncthreads();
+#pragma unroll
+		for (int k = 0; k < BK; k++) {
+			const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+			const float4 b = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+			const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+			for (int i = 0; i < 4; i++)
+#pragma unroll
+				for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int i = 0; i < 4; i++) {
+		const int row = m0 + ty * 4 + i;
+		if (row >= T) continue;
+		if (e.kind == EPI_GLU) {
+#pragma unroll
+			for (int j = 0; j < 4; j += 2) {
+				const int col = n0 + tx * 4 + j;
+				if (col + 1 < N) epi_apply(e, row, col, N, acc[i][j], acc[i][j + 1]);
+			}
+		} else {
+#pragma unroll
+			for (int j = 0; j < 4; j++) {
+				const int col = n0 + tx * 4 + j;
+				if (col < N) epi_apply(e, row, col, N, acc[i][j], 0.f);
+			}
+		}
+	}
+}
+
+// ---- the same for T <= TB tokens: a warp per pair of output columns -------------------------------------------------------------
+template <typename WT, int TB>
+__global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
+	const int lane = threadIdx.x & 31;
+	const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+	const int c0 = pair * 2;
+	if (c0 >= N) return;
+	const bool two = c0 + 1 < N;
+	const WT* w0 = W + (size_t) c0 * K;
+	const WT* w1 = W + (size_t) (two ? c0 + 1 : c0) * K;
+	float acc0[TB] = {}, acc1[TB] = {};
+	const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+	if (vec) {
+		for (int k = lane * 8; k < K; k += 256) {
+			float a0[8], a1[8];
+			ld8(w0 + k, a0);
+			ld8(w1 + k, a1);
+#pragma unroll
+			for (int t = 0; t < TB; t++) {
+				if (t < T) {
+					float x[8];
+					ld8(A + (size_t) t * lda + k, x);
+#pragma unroll
+					for (int i = 0; i < 8; i++) {
+						acc0[t] = fmaf(a0[i], x[i], acc0[t]);
+						acc1[t] = fmaf(a1[i], x[i], acc1[t]);
+					}
+				}
+			}
+		}
+	} else {
+		for (int k = lane; k < K; k += 32) {
+			const float a0 = ldf(w0 + k), a1 = ldf(w1 + k);
+#pragma unroll
+			for (int t = 0; t < TB; t++)
+				if (t < T) {
+					const float x = A[(size_t) t * lda + k];
+					acc0[t] = fmaf(a0, x, acc0[t]);
+					acc1[t] = fmaf(a1, x, acc1[t]);
+				}
+		}
+	}
+#pragma unroll
+	for (int t = 0; t < TB; t++) {
+		acc0[t] = warp_sum(acc0[t]);
+		acc1[t] = warp_sum(acc1[t]);
+	}
+	if (lane == 0) {
+#pragma unroll
+		for (int t = 0; t < TB; t++) {
+			if (t >= T) break;
+			if (e.kind == EPI_GLU) {
+				if (two) epi_apply(e, t, c0, N, acc0[t], acc1[t]);
+			} else {
+				epi_apply(e, t, c0, N, acc0[t], 0.f);
+				if (two) epi_apply(e, t, c0 + 1, N, acc1[t], 0.f);
+			}
+		}
+	}
+}
+
+// ---- sliding-window softmax attention with score mixing across heads -------------------------------------------------------------
+struct SwaArgs {
+	const float* q;    // (T, ldq): head h at columns q_off + h * d
+	const float* gate; // (T, ldq): pre-sigmoid gate of the concatenated heads at columns g_off + ...; NULL: no gate
+	int ldq, q_off, g_off;
+	const void* kc;    // ring (ring, G * d)
+	const void* vc;    // ring (ring, G * dv)
+	int ring;
+	int H, G, d, dv;
+	int window;        // position i sees j with 0 <= i - j < window
+	float scale;
+	float softcap;     // 0: none
+	const float* r1;   // distance bias r1[h] * log1p(r2[h] * (i - j)) taken off the score; NULL: none
+	const float* r2;
+	const float* talk; // (H, H) score_h <- sum_g talk[h, g] score_g; NULL: none
+	const SeqStep* step;
+	float* out;        // (T, H * dv)
+	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes
+	float* part_o;     // (T, n_splits, H * dv)
+	float* part_ml;    // (T, n_splits, H, 2)
+};
+
+constexpr int SWA_KB = 32; // keys per block
+
+template <typename CT>
+__global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
+	extern __shared__ float sm[];
+	const int H = a.H, G = a.G, d = a.d, dv = a.dv, rep = H / G;
+	float* qs = sm;                  // H * d
+	float* sc = qs + H * d;          // H * KB raw scores
+	float* pr = sc + H * SWA_KB;     // H * KB mixed scores, then probabilities
+	float* tk = pr + H * SWA_KB;     // H * H
+	float* mrun = tk + H * H;        // H
+	float* lrun = mrun + H;          // H
+	float* alpha = lrun + H;         // H
+	float* O = alpha + H;            // H * dv
+	const CT* kc = reinterpret_cast<const CT*>(a.kc);
+	const CT* vc = reinterpret_cast<const CT*>(a.vc);
+	const int t = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, nth = blockDim.x;
+	const int i = a.step->pos0 + t;
+	const int j_first = max(0, i - a.window + 1);
+	const int nk = i - j_first + 1;
+	int per = (nk + a.n_splits - 1) / a.n_splits;
+	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
+	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
+
+	for (int x = tid; x < H * d; x += nth) qs[x] = a.q[(size_t) t * a.ldq + a.q_off + x];
+	for (int x = tid; x < H * H; x += nth) tk[x] = a.talk ? a.talk[x] : (x / H == x % H ? 1.f : 0.f);
+	for (int x = tid; x < H; x += nth) { mrun[x] = -INFINITY; lrun[x] = 0.f; }
+	for (int x = tid; x < H * dv; x += nth) O[x] = 0.f;
+	__syncthreads();
+
+	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
+		const int nb = min(SWA_KB, je - j0);
+		// raw scores: scale, soft cap, distance bias
+		for (int x = tid; x < H * SWA_KB; x += nth) {
+			const int h = x / SWA_KB, jj = x % SWA_KB;
+			float s = 0.f;
+			if (jj < nb) {
+				const int j = j0 + jj;
+				const CT* kr = kc + (size_t) (j % a.ring) * (G * d) + (h / rep) * d;
+				const float* qh = qs + h * d;
+				float acc = 0.f;
+				for (int c = 0; c < d; c++) acc = fmaf(qh[c], ldf(kr + c), acc);
+				s = acc * a.scale;
+				if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+				if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) (i - j));
+			}
+			sc[x] = s;
+		}
+		__syncthreads();
+		// mix the heads' scores
+		for (int x = tid; x < H * SWA_KB; x += nth) {
+			const int h = x / SWA_KB, jj = x % SWA_KB;
+			float s = -INFINITY;
+			if (jj < nb) {
+				if (a.talk) {
+					s = 0.f;
+					for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * SWA_KB + jj], s);
+				} else s = sc[x];
+			}
+			pr[x] = s;
+		}
+		__syncthreads();
+		// online softmax, a warp per head
+		for (int h = tid >> 5; h < H; h += nth >> 5) {
+			const int lane = tid & 31;
+			const float s = pr[h * SWA_KB + lane]; // SWA_KB == 32
+			const float bm = warp_max(s);
+			const float m_old = mrun[h], m_new = fmaxf(m_old, bm);
+			const float p = (lane < nb) ? expf(s - m_new) : 0.f;
+			const float ps = warp_sum(p);
+			pr[h * SWA_KB + lane] = p;
+			if (lane == 0) {
+				const float al = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+				alpha[h] = al;
+				mrun[h] = m_new;
+				lrun[h] = lrun[h] * al + ps;
+			}
+		}
+		__syncthreads();
+		// O <- alpha O + P V
+		for (int x = tid; x < H * dv; x += nth) {
+			const int h = x / dv, c = x % dv;
+			float acc = O[x] * alpha[h];
+			const CT* vcol = vc + (h / rep) * dv + c;
+			const float* ph = pr + h * SWA_KB;
+			for (int jj = 0; jj < nb; jj++) acc = fmaf(ph[jj], ldf(vcol + (size_t) ((j0 + jj) % a.ring) * (G * dv)), acc);
+			O[x] = acc;
+		}
+		__syncthreads();
+	}
+	if (a.n_splits == 1) {
+		for (int x = tid; x < H * dv; x += nth) {
+			float o = O[x] / lrun[x / dv];
+			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldq + a.g_off + x]);
+			a.out[(size_t) t * (H * dv) + x] = o;
+		}
+	} else {
+		float* po = a.part_o + ((size_t) t * a.n_splits + sp) * (H * dv);
+		float* pml = a.part_ml + ((size_t) t * a.n_splits + sp) * (H * 2);
+		for (int x = tid; x < H * dv; x += nth) po[x] = O[x];
+		for (int x = tid; x < H; x += nth) { pml[2 * x] = mrun[x]; pml[2 * x + 1] = lrun[x]; }
+	}
+}
+
+inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
+
+// joins the key splits of one-token steps: out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
+__global__ void swa_merge_kernel(SwaArgs a) {
+	const int t = blockIdx.x, H = a.H, dv = a.dv;
+	for (int x = threadIdx.x; x < H * dv; x += blockDim.x) {
+		const int h = x / dv;
+		float m = -INFINITY;
+		for (int s = 0; s < a.n_splits; s++) m = fmaxf(m, a.part_ml[((size_t) t * a.n_splits + s) * (H * 2) + 2 * h]);
+		float num = 0.f, den = 0.f;
+		for (int s = 0; s < a.n_splits; s++) {
+			const float* pml = a.part_ml + ((size_t) t * a.n_splits + s) * (H * 2);
+			const float ms = pml[2 * h];
+			if (ms == -INFINITY) continue;
+			const float w = expf(ms - m);
+			num = fmaf(w, a.part_o[((size_t) t * a.n_splits + s) * (H * dv) + x], num);
+			den = fmaf(w, pml[2 * h + 1], den);
+		}
+		float o = num / den;
+		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldq + a.g_off + x]);
+		a.out[(size_t) t * (H * dv) + x] = o;
+	}
+}
+
+// ---- gated linear recurrence (HGRN2) --------------------------------------------------------------------------------------------
+struct Hgrn2Args {
+	const float* proj; // (T, ld): per head h, q at q_off + h * d, forget pre-activation at f_off + h * d, v at v_off + h * dv
+	int ld, q_off, f_off, v_off;
+	int H, d, dv;
+	const float* f_bias; // (H * d) or NULL
+	const float* lower;  // (H * d) lower bound of the forget gate, or NULL (0)
+	const float* norm_w; // (dv) plain weight of the per-head RMS norm of o, or NULL (no norm)
+	float eps;
+	float* state;        // (H, d, dv) fp32, carried between steps
+	const SeqStep* step;
+	float* out;          // (T, H * dv)
+};
+constexpr int HG_TC = 8; // tokens staged at a time
+
+__global__ void hgrn2_kernel(Hgrn2Args a) {
+	extern __shared__ float sm[];
+	const int d = a.d, dv = a.dv, h = blockIdx.x, tid = threadIdx.x, nth = blockDim.x;
+	float* S = sm;                  // d * dv
+	float* fch = S + (size_t) d * dv; // TC * d
+	float* qch = fch + HG_TC * d;   // TC * d
+	float* och = qch + HG_TC * d;   // TC * dv
+	float* st = a.state + (size_t) h * d * dv;
+	for (int x = tid; x < d * dv; x += nth) S[x] = st[x];
+	const int T = a.step->n;
+	for (int t0 = 0; t0 < T; t0 += HG_TC) {
+		const int nt = min(HG_TC, T - t0);
+		__syncthreads();
+		for (int x = tid; x < nt * d; x += nth) {
+			const int tt = x / d, i = x % d;
+			const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
+			const float z = row[a.f_off + h * d + i] + (a.f_bias ? a.f_bias[h * d + i] : 0.f);
+			const float lo = a.lower ? a.lower[h * d + i] : 0.f;
+			fch[x] = lo + (1.f - lo) * sigmoidf_(z);
+			const float zq = row[a.q_off + h * d + i];
+			qch[x] = zq * sigmoidf_(zq);
+		}
+		__syncthreads();
+		for (int c = tid; c < dv; c += nth) {
+			for (int tt = 0; tt < nt; tt++) {
+				const float v = a.proj[(size_t) (t0 + tt) * a.ld + a.v_off + h * dv + c];
+				const float* f = fch + tt * d;
+				const float* q = qch + tt * d;
+				float o = 0.f;
+				for (int i = 0; i < d; i++) {
+					const float fi = f[i];
+					const float s = fmaf(fi, S[(size_t) i * dv + c], (1.f - fi) * v);
+					S[(size_t) i * dv + c] = s;
+					o = fmaf(s, q[i], o);
+				}
+				och[tt * dv + c] = o;
+			}
+		}
+		__syncthreads();
+		for (int tt = tid >> 5; tt < nt; tt += nth >> 5) {
+			const int lane = tid & 31;
+			float r = 1.f;
+			if (a.norm_w) {
+				float ss = 0.f;
+				for (int c = lane; c < dv; c += 32) ss = fmaf(och[tt * dv + c], och[tt * dv + c], ss);
+				ss = warp_sum(ss);
+				r = 1.f / sqrtf(ss / (float) dv + a.eps);
+			}
+			float* orow = a.out + (size_t) (t0 + tt) * (a.H * dv) + h * dv;
+			for (int c = lane; c < dv; c += 32) orow[c] = och[tt * dv + c] * r * (a.norm_w ? a.norm_w[c] : 1.f);
+		}
+	}
+	__syncthreads();
+	for (int x = tid; x < d * dv; x += nth) st[x] = S[x];
+}
+inline size_t hgrn2_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t) d * dv + 2 * (size_t) HG_TC * d + (size_t) HG_TC * dv); }
+
+// ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
+__global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
+                                    float eps, int width, RowsEpi e) {
+	extern __shared__ float sm[];
+	float* red = sm;
+	const int t = blockIdx.x;
+	float sa = 0.f, sb = 0.f;
+	for (int c = threadIdx.x; c < width; c += blockDim.x) {
+		const float x = A[(size_t) t * width + c], y = B[(size_t) t * width + c];
+		sa = fmaf(x, x, sa);
+		sb = fmaf(y, y, sb);
+	}
+	const float ra = 1.f / sqrtf(block_sum(sa, red) / (float) width + eps);
+	const float rb = 1.f / sqrtf(block_sum(sb, red) / (float) width + eps);
+	for (int c = threadIdx.x; c < width; c += blockDim.x) {
+		const float y = 0.5f * (A[(size_t) t * width + c] * ra * wa[c] + B[(size_t) t * width + c] * rb * wb[c]);
+		hc_write(e, t, c, width, y);
+	}
+}
+
+} // namespace mix
+} // namespace xalm

@@ -19,7 +19,11 @@ import ctypes as C
 
 import numpy as np
 
+import json
+import os
+
 from . import capi
+from . import safetensors_io as ST
 from . import types as T
 from . import xalm_file as X
 
@@ -86,9 +90,80 @@ class Model:
                 tensors[name] = (t, tuple(shapes[name]), np.ascontiguousarray(arr).view(np.uint8).reshape(-1))
         return Model(config, tensors)
 
+    # ---- model folders described by a config.json ("architecture": "<family>") + model.safetensors ------------------------
+    @staticmethod
+    def from_pretrained(path: str) -> "Model":
+        """The backend picks the model family by the config's "architecture" and parses the JSON itself; the host side only
+        carries the text and the tensors (integer tables are not uploaded)."""
+        with open(os.path.join(path, "config.json")) as f:
+            text = f.read()
+        tensors = {n: v for n, v in ST.read_tensors(os.path.join(path, "model.safetensors")).items() if v[0] is not None}
+        return Model._from_json_text(text, tensors)
+
+    @staticmethod
+    def from_json(config: dict, arrays: "dict[str, np.ndarray]", dtype: str = "BF16") -> "Model":
+        """The same from a config dict and fp32 arrays held in memory, stored as `dtype` (BF16 or F32) for the upload."""
+        tensors = {}
+        for name, a in arrays.items():
+            a = np.ascontiguousarray(a, dtype=np.float32)
+            raw = ST.f32_to_bf16_bits(a) if dtype == "BF16" else a
+            tensors[name] = (T.BF16 if dtype == "BF16" else T.F32, tuple(a.shape), raw.view(np.uint8).reshape(-1))
+        return Model._from_json_text(json.dumps(config), tensors)
+
+    @staticmethod
+    def _from_json_text(text: str, tensors) -> "Model":
+        c = json.loads(text)
+        if not isinstance(c.get("architecture"), str):
+            raise ValueError("config.json names no architecture")
+        config = {"architecture": c["architecture"], "json": text, "vocab_size": int(c.get("vocab", c.get("vocab_size", 0)))}
+        return Model(config, tensors)
+
+    def _cuda_json(self, device: int, max_tokens: int, precision: int, stream) -> "Model":
+        L = capi.lib()
+        h = C.c_void_p()
+        capi.check(L.xalm_cuda_create_json(self.config["json"].encode(), device, int(max_tokens), int(precision), C.byref(h)))
+        self._h = h
+        try:
+            if stream is not None:
+                capi.check(L.xalm_cuda_set_stream(h, C.c_void_p(stream)))
+            for name in self.expected_tensors():
+                if name in self.tensors:
+                    t, shape, raw = self.tensors[name]
+                    self.upload(name, t, shape, raw)
+            capi.check(L.xalm_cuda_finalize(h))
+            for key in ("vocab_size", "dim", "n_layers", "max_tokens"):
+                self.config[key] = self.info(key)
+            self.config["max_seq_len"] = self.config["max_tokens"]
+        except Exception:
+            self.close()
+            raise
+        return self
+
+    def expected_tensors(self) -> "dict[str, tuple]":
+        """name -> element shape of every tensor the family reads (config.json families)."""
+        out, i = {}, 0
+        name, shape, rank = C.create_string_buffer(256), (C.c_int * 4)(), C.c_int(0)
+        while capi.lib().xalm_cuda_expected_tensor(self._h, i, name, 256, shape, C.byref(rank)) == 0:
+            out[name.value.decode()] = tuple(shape[: rank.value])
+            i += 1
+        return out
+
+    def info(self, key: str) -> int:
+        v = C.c_longlong(0)
+        capi.check(capi.lib().xalm_cuda_model_info(self._h, key.encode(), C.byref(v)))
+        return v.value
+
+    def release(self) -> None:
+        """The running sequence is over: what it holds in the cache and the recurrent state is given back."""
+        capi.check(capi.lib().xalm_cuda_release(self._h))
+
     # ---- model.cuda() -----------------------------------------------------------------------------------------
     def cuda(self, device: int = 0, tp_rank: int = 0, tp_size: int = 1, comm_id: bytes | None = None, stream: int | None = None,
-             release_host: bool = False, ipc_exchange=None) -> "Model":
+             release_host: bool = False, ipc_exchange=None, max_tokens: int = 4096, precision: int = capi.PRECISION_BF16) -> "Model":
+        if "json" in self.config:
+            if tp_size != 1:
+                raise ValueError("config.json families run on one GPU")
+            return self._cuda_json(device, max_tokens, precision, stream)
         L = capi.lib()
         h = C.c_void_p()
         cfg = capi.XalmConfig.from_dict(self.config)
@@ -224,6 +299,25 @@ class Model:
             self.close()
         except Exception:
             pass
+
+
+def generate(model: "Model", state: "InferenceState", sampler: "Sampler", prompt, steps: int, portion: int = 0) -> list:
+    """Greedy completion as the command line runs it (main.cpp:94-115): the prompt in one batched pass (or in portions of
+    `portion` tokens), then one forward per sampled token.  Returns prompt + generated ids."""
+    seq = [int(t) for t in prompt]
+    pos = 0
+    while pos < len(seq):
+        n = len(seq) - pos if portion <= 0 else min(portion, len(seq) - pos)
+        last = pos + n == len(seq)
+        lg = model.prefill(seq[pos:pos + n], pos, 1 if last else 0)
+        if last:
+            state.logits()[:] = lg
+        pos += n
+    for _ in range(steps):
+        tok = sampler.sample_argmax(state)
+        seq.append(tok)
+        model.forward(state, tok, len(seq) - 1)
+    return seq
 
 
 def active_bytes_formula(c: dict, bytes_per_weight: float, pos: int, emb_bpw: float | None = None, norm_bytes: int = 4) -> int:
