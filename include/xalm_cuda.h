@@ -125,6 +125,33 @@ int xalm_cuda_expected_tensor(xalm_cuda_model* m, int index, char* name, size_t 
 /* Integer properties by name: "vocab_size", "dim", "n_layers", "max_tokens", "position" (tokens the sequence holds). */
 int xalm_cuda_model_info(xalm_cuda_model* m, const char* key, long long* value);
 
+/* ---- mechanism ops: the sequence-mixing kernels of the config.json families, one call each (host arrays in and out, fp32) -----
+ * They launch the kernels the families run, so a test holds each mechanism against a plain restatement.
+ *
+ * swa_attention: softmax attention over a sliding window (position i sees j with 0 <= i - j < window) for the T positions
+ *   pos0 .. pos0+T-1.  q (T, H*d); k (pos0+T, G*d) and v (pos0+T, G*dv) hold EVERY position from 0 — the call lays them into a
+ *   ring of `ring` slots (slot = position mod ring) as the cache manager would, so positions older than the ring are gone.
+ *   score = scale q.k -> softcap * tanh(./softcap) (softcap 0: none) -> minus r1[h] * log1p(r2[h] (i - j)) (r1/r2 NULL: none) ->
+ *   mixed across heads by talk (H, H) (NULL: none) -> softmax -> times v -> times sigmoid(gate (T, H*dv)) (NULL: none).
+ *   n_splits > 1 splits the keys over CTAs as one-token steps do; cache_bf16 stores the ring in bf16.
+ * hgrn2: S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t per head, q = silu(qz), f = lower + (1 - lower) sigmoid(fz + f_bias)
+ *   (f_bias / lower NULL: 0), o RMS-normed over dv with norm_w (NULL: no norm).  qz, fz (T, H*d); v (T, H*dv); state (H, d, dv) is
+ *   read and written; out (T, H*dv).
+ * hyper_norm: h[t] = rmsnorm(sum_s a[s] xs[s][t]) * (one_plus ? 1 + w : w); xs (S, T, W); a NULL: every coefficient 1.
+ * dual_norm_hyper: y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb); xs[t'] <- sum_s mix[s, t'] xs[s] + out_coef[t'] * scale * y, all streams
+ *   from the old ones (mix NULL: identity; out_coef NULL: ones; scale NULL: none).  xs (S, T, W) is read and written.
+ * glu_rows: out (T, ff) = g * sigmoid(alpha g) * (u + 1), g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit); w_bf16 rounds the
+ *   weights to bf16 first (the serving layout). */
+int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv,
+                            int window, float scale, float softcap, const float* r1, const float* r2, const float* talk, int ring, int n_splits,
+                            int cache_bf16);
+int xalm_cuda_hgrn2(float* out, float* state, const float* qz, const float* fz, const float* v, int T, int H, int d, int dv, const float* f_bias,
+                    const float* lower, const float* norm_w, float eps);
+int xalm_cuda_hyper_norm(float* h, const float* xs, int S, int T, int W, const float* a, const float* w, int one_plus, float eps);
+int xalm_cuda_dual_norm_hyper(float* xs, const float* a, const float* b, const float* wa, const float* wb, float eps, int S, int T, int W,
+                              const float* mix, const float* out_coef, const float* scale);
+int xalm_cuda_glu_rows(float* out, const float* x, const float* w_gate, const float* w_up, int T, int ff, int K, float limit, float alpha, int w_bf16);
+
 /* Tensor parallel plumbing (no reference analogue; north star).  Rank 0 makes an id, the host side ships it to
  * the other ranks (torch.distributed / MPI / a file), every rank calls comm_init before finalize. */
 #define XALM_COMM_ID_BYTES 128

@@ -86,6 +86,11 @@ SYMBOLS = {
     "xalm_cuda_release": (_i, [_vp]),
     "xalm_cuda_expected_tensor": (_i, [_vp, _i, C.c_char_p, _sz, C.POINTER(_i), C.POINTER(_i)]),
     "xalm_cuda_model_info": (_i, [_vp, C.c_char_p, C.POINTER(C.c_longlong)]),
+    "xalm_cuda_swa_attention": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, C.c_float, C.c_float, _vp, _vp, _vp, _i, _i, _i]),
+    "xalm_cuda_hgrn2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, C.c_float]),
+    "xalm_cuda_hyper_norm": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, C.c_float]),
+    "xalm_cuda_dual_norm_hyper": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_float, _i, _i, _i, _vp, _vp, _vp]),
+    "xalm_cuda_glu_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, C.c_float, _i]),
 }
 PRECISION_BF16, PRECISION_F32 = 0, 1            # enum xalm_precision
 
@@ -125,6 +130,14 @@ def device_count() -> int:
     n = C.c_int(0)
     check(lib().xalm_cuda_device_count(C.byref(n)))
     return n.value
+
+
+def device_count_or_zero() -> int:
+    """CUDA devices this process can use; 0 when there is no driver."""
+    try:
+        return device_count()
+    except XalmError:
+        return 0
 
 
 def families() -> list:
@@ -229,3 +242,59 @@ def bench_gemm(T: int, N: int, K: int, split: int = 1, iters: int = 20) -> float
     ms = C.c_float(0)
     check(lib().xalm_cuda_bench_gemm(T, N, K, split, iters, C.byref(ms)))
     return ms.value
+
+
+# ---- mechanism ops of the config.json families (include/xalm_cuda.h, "mechanism ops") --------------------------------------
+def _f(a):
+    return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _pn(a):
+    return None if a is None else _p(a)
+
+
+def swa_attention(q, k, v, pos0, H, G, d, dv, window, scale, softcap=0.0, r1=None, r2=None, talk=None, gate=None, ring=None,
+                  n_splits=1, cache_bf16=False):
+    q, k, v, gate, r1, r2, talk = _f(q), _f(k), _f(v), _f(gate), _f(r1), _f(r2), _f(talk)
+    T = q.shape[0]
+    if ring is None:
+        ring = min(pos0 + T, window - 1 + T)
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_swa_attention(_p(out), _p(q), _pn(gate), _p(k), _p(v), T, pos0, H, G, d, dv, window, scale, softcap, _pn(r1), _pn(r2),
+                                        _pn(talk), ring, n_splits, int(cache_bf16)))
+    return out
+
+
+def hgrn2(qz, fz, v, state, H, d, dv, f_bias=None, lower=None, norm_w=None, eps=1e-5):
+    """Returns (out, new state); `state` (H, d, dv) is not modified."""
+    qz, fz, v, f_bias, lower, norm_w = _f(qz), _f(fz), _f(v), _f(f_bias), _f(lower), _f(norm_w)
+    st = np.array(state, dtype=np.float32, copy=True)
+    T = qz.shape[0]
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_hgrn2(_p(out), _p(st), _p(qz), _p(fz), _p(v), T, H, d, dv, _pn(f_bias), _pn(lower), _pn(norm_w), eps))
+    return out, st
+
+
+def hyper_norm(xs, a, w, one_plus, eps):
+    xs, a, w = _f(xs), _f(a), _f(w)
+    S, T, W = xs.shape
+    h = np.empty((T, W), dtype=np.float32)
+    check(lib().xalm_cuda_hyper_norm(_p(h), _p(xs), S, T, W, _pn(a), _p(w), int(one_plus), eps))
+    return h
+
+
+def dual_norm_hyper(xs, a, b, wa, wb, eps, mix=None, out_coef=None, scale=None):
+    xs = np.array(xs, dtype=np.float32, copy=True)
+    a, b, wa, wb, mix, out_coef, scale = _f(a), _f(b), _f(wa), _f(wb), _f(mix), _f(out_coef), _f(scale)
+    S, T, W = xs.shape
+    check(lib().xalm_cuda_dual_norm_hyper(_p(xs), _p(a), _p(b), _p(wa), _p(wb), eps, S, T, W, _pn(mix), _pn(out_coef), _pn(scale)))
+    return xs
+
+
+def glu_rows(x, w_gate, w_up, limit, alpha=1.702, w_bf16=False):
+    x, w_gate, w_up = _f(x), _f(w_gate), _f(w_up)
+    T, K = x.shape
+    ff = w_gate.shape[0]
+    out = np.empty((T, ff), dtype=np.float32)
+    check(lib().xalm_cuda_glu_rows(_p(out), _p(x), _p(w_gate), _p(w_up), T, ff, K, limit, alpha, int(w_bf16)))
+    return out

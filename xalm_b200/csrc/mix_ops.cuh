@@ -16,6 +16,9 @@
 //                          forget gate, state in fp32 carried in device memory, per-head RMS norm of o fused
 //   dual_norm_hc_kernel    y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb) -> layer scale -> hyper-connection write
 //
+// The kernels have internal linkage: every translation unit that includes this header (a model family, the op-level entry points
+// of mix_ops.cu) gets its own copies.
+//
 // Numerics: everything here is fp32 (expf / tanhf / log1pf, no fast-math); 16-bit storage appears only as weight and K/V-cache
 // element types.
 #pragma once
@@ -23,6 +26,8 @@
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
+
+#include <algorithm>
 
 #include "common.cuh"
 
@@ -87,7 +92,7 @@ __global__ void embed_streams_kernel(const WT* __restrict__ table, const int* __
 // ---- hyper-connection read + RMS norm -------------------------------------------------------------------------------------
 // h[t] = rmsnorm(sum_s a[s] xs[s][t]) * (one_plus ? 1 + w : w).  a == nullptr: every coefficient is 1 (the final sum of streams).
 // `sum_out` (optional) receives the un-normed combination (the residual stream as a reader outside the model sees it).
-__global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t stream_stride, const float* __restrict__ a, const float* __restrict__ w,
+static __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t stream_stride, const float* __restrict__ a, const float* __restrict__ w,
                                int one_plus, float eps, int width, float* __restrict__ h, float* __restrict__ sum_out) {
 	extern __shared__ float sm[];
 	float* u = sm;            // width
@@ -293,8 +298,8 @@ __global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restric
 // ---- sliding-window softmax attention with score mixing across heads -------------------------------------------------------------
 struct SwaArgs {
 	const float* q;    // (T, ldq): head h at columns q_off + h * d
-	const float* gate; // (T, ldq): pre-sigmoid gate of the concatenated heads at columns g_off + ...; NULL: no gate
-	int ldq, q_off, g_off;
+	const float* gate; // (T, ldg): pre-sigmoid gate of the concatenated heads at columns g_off + ...; NULL: no gate
+	int ldq, q_off, ldg, g_off;
 	const void* kc;    // ring (ring, G * d)
 	const void* vc;    // ring (ring, G * dv)
 	int ring;
@@ -405,7 +410,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	if (a.n_splits == 1) {
 		for (int x = tid; x < H * dv; x += nth) {
 			float o = O[x] / lrun[x / dv];
-			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldq + a.g_off + x]);
+			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
 			a.out[(size_t) t * (H * dv) + x] = o;
 		}
 	} else {
@@ -419,7 +424,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
 
 // joins the key splits of one-token steps: out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
-__global__ void swa_merge_kernel(SwaArgs a) {
+static __global__ void swa_merge_kernel(SwaArgs a) {
 	const int t = blockIdx.x, H = a.H, dv = a.dv;
 	for (int x = threadIdx.x; x < H * dv; x += blockDim.x) {
 		const int h = x / dv;
@@ -435,7 +440,7 @@ __global__ void swa_merge_kernel(SwaArgs a) {
 			den = fmaf(w, pml[2 * h + 1], den);
 		}
 		float o = num / den;
-		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldq + a.g_off + x]);
+		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
 		a.out[(size_t) t * (H * dv) + x] = o;
 	}
 }
@@ -455,7 +460,7 @@ struct Hgrn2Args {
 };
 constexpr int HG_TC = 8; // tokens staged at a time
 
-__global__ void hgrn2_kernel(Hgrn2Args a) {
+static __global__ void hgrn2_kernel(Hgrn2Args a) {
 	extern __shared__ float sm[];
 	const int d = a.d, dv = a.dv, h = blockIdx.x, tid = threadIdx.x, nth = blockDim.x;
 	float* S = sm;                  // d * dv
@@ -513,7 +518,7 @@ __global__ void hgrn2_kernel(Hgrn2Args a) {
 inline size_t hgrn2_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t) d * dv + 2 * (size_t) HG_TC * d + (size_t) HG_TC * dv); }
 
 // ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
-__global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
+static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
                                     float eps, int width, RowsEpi e) {
 	extern __shared__ float sm[];
 	float* red = sm;
@@ -530,6 +535,90 @@ __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __
 		const float y = 0.5f * (A[(size_t) t * width + c] * ra * wa[c] + B[(size_t) t * width + c] * rb * wb[c]);
 		hc_write(e, t, c, width, y);
 	}
+}
+
+// ---- host-side launchers (shared by the model families and the op-level entry points) ------------------------------------------
+static inline int launch_check(const char* what) {
+	const cudaError_t e = cudaGetLastError();
+	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+	return XALM_OK;
+}
+static inline int norm_threads(int width) { return width >= 1024 ? 256 : width >= 256 ? 128 : 64; }
+
+// out(T,N) = A(T,K) . W(N,K)^T with epilogue e, IEEE fp32 arithmetic; W is bf16 or fp32
+static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf16, int T, int N, int K, const RowsEpi& e, cudaStream_t s) {
+	if (T <= 4) {
+		const int pairs = (N + 1) / 2, grid = (pairs + 7) / 8;
+		if (w_bf16) {
+			if (T == 1) rows_matvec_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
+			else rows_matvec_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
+		} else {
+			if (T == 1) rows_matvec_kernel<float, 1><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
+			else rows_matvec_kernel<float, 4><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
+		}
+	} else {
+		const dim3 grid((N + 63) / 64, (T + 63) / 64);
+		if (w_bf16) rows_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
+		else rows_gemm_kernel<float><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
+	}
+	return launch_check("row product");
+}
+
+// Kernels whose shared memory can pass 48 KB raise their limit once per process (these families run on one device).  A family calls
+// the prepare functions when it finalizes, so that no attribute changes while a step is captured into a graph.
+static inline int hc_norm_prepare(int width) {
+	static bool raised = false;
+	if ((size_t) (width + 33) * 4 > 48 * 1024 && !raised) {
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		raised = true;
+	}
+	return XALM_OK;
+}
+static inline int swa_prepare(int H, int d, int dv) {
+	static bool raised = false;
+	if (swa_smem_bytes(H, d, dv) > 48 * 1024 && !raised) {
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		raised = true;
+	}
+	return XALM_OK;
+}
+static inline int hgrn2_prepare(int d, int dv) {
+	static bool raised = false;
+	if (hgrn2_smem_bytes(d, dv) > 48 * 1024 && !raised) {
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		raised = true;
+	}
+	return XALM_OK;
+}
+
+static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, const float* a, const float* w, int one_plus, float eps, int width, float* h,
+                          float* sum_out, int rows, cudaStream_t s) {
+	const size_t smem = (size_t) (width + 33) * 4;
+	XALM_TRY(hc_norm_prepare(width));
+	hc_norm_kernel<<<rows, norm_threads(width), smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
+	return launch_check("hc_norm");
+}
+
+// rows: tokens of the step; cache_f32: element type of the ring.  With n_splits > 1 the merge kernel follows.
+static inline int launch_swa(const SwaArgs& a, int rows, bool cache_f32, cudaStream_t s) {
+	const size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
+	XALM_TRY(swa_prepare(a.H, a.d, a.dv));
+	if (cache_f32) swa_attn_kernel<float><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
+	else swa_attn_kernel<__nv_bfloat16><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
+	XALM_TRY(launch_check("swa_attn"));
+	if (a.n_splits > 1) {
+		swa_merge_kernel<<<rows, 256, 0, s>>>(a);
+		XALM_TRY(launch_check("swa_merge"));
+	}
+	return XALM_OK;
+}
+
+static inline int launch_hgrn2(const Hgrn2Args& a, cudaStream_t s) {
+	const size_t smem = hgrn2_smem_bytes(a.d, a.dv);
+	XALM_TRY(hgrn2_prepare(a.d, a.dv));
+	hgrn2_kernel<<<a.H, std::min(1024, (a.dv + 31) / 32 * 32), smem, s>>>(a);
+	return launch_check("hgrn2");
 }
 
 } // namespace mix

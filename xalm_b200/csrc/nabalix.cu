@@ -303,28 +303,11 @@ int upload_rows(Nb* m, const std::vector<const HostTensor*>& parts, int K, bool 
 	return XALM_OK;
 }
 
-// ---- row products: fp32 FMA kernels, or the tcgen05 GEMM for the 16-bit mode's large passes -------------------------------------
+// ---- row products: fp32 FMA kernels (mix_ops.cuh) -----------------------------------------------------------------------------
 int rows_product(Nb* m, const float* A, int lda, const void* W, const WMat* wm, int T, int N, int K, const RowsEpi& e, int* nl) {
-	cudaStream_t s = m->stream;
-	if (T <= 4) {
-		const int pairs = (N + 1) / 2, grid = (pairs + 7) / 8;
-		if (m->w_bf16) {
-			if (T == 1) rows_matvec_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
-			else rows_matvec_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
-		} else {
-			if (T == 1) rows_matvec_kernel<float, 1><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
-			else rows_matvec_kernel<float, 4><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
-		}
-	} else {
-		(void) wm;
-		const dim3 grid((N + 63) / 64, (T + 63) / 64);
-		if (m->w_bf16) rows_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
-		else rows_gemm_kernel<float><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
-	}
+	(void) wm;
 	(*nl)++;
-	cudaError_t err = cudaGetLastError();
-	if (err != cudaSuccess) return set_error(XALM_ERR_CUDA, "row product launch failed: %s", cudaGetErrorString(err));
-	return XALM_OK;
+	return launch_rows(A, lda, W, m->w_bf16, T, N, K, e, m->stream);
 }
 
 #define NB_LAUNCH_CHECK(what)                                                                                       \
@@ -352,8 +335,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 	cudaStream_t s = m->stream;
 	const int W = m->width, S = m->S;
 	const size_t sstride = (size_t) m->chunk * W;
-	const int rt = std::min(256, std::max(32, (W + 31) / 32 * 32));
-	const size_t norm_smem = (size_t) (W + 33) * 4;
+	const int rt = norm_threads(W);
 	if (m->w_bf16) embed_streams_kernel<__nv_bfloat16><<<n, rt, 0, s>>>((const __nv_bfloat16*) m->embed, m->d_tokens, W, S, sstride, m->xs);
 	else embed_streams_kernel<float><<<n, rt, 0, s>>>((const float*) m->embed, m->d_tokens, W, S, sstride, m->xs);
 	NB_LAUNCH_CHECK("embed");
@@ -361,8 +343,8 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		const Layer& L = m->layers[li];
 		const int H = L.L.H, G = L.L.G, d = L.L.d, dv = L.L.dv, Hr = L.R.H, dr = L.R.d, dvr = L.R.dv;
 		// ---- mixer ----
-		hc_norm_kernel<<<n, rt, norm_smem, s>>>(m->xs, S, sstride, L.hc_in[0], L.norm1, 1, m->eps, W, m->h, nullptr);
-		NB_LAUNCH_CHECK("hc_norm");
+		XALM_TRY(launch_hc_norm(m->xs, S, sstride, L.hc_in[0], L.norm1, 1, m->eps, W, m->h, nullptr, n, s));
+		(*nl)++;
 		RowsEpi ein;
 		ein.kind = EPI_SPLIT_KV;
 		ein.out = m->proj;
@@ -373,7 +355,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		XALM_TRY(rows_product(m, m->h, W, L.w_in, &L.m_in, n, L.n_in, W, ein, nl));
 		SwaArgs sa = {};
 		sa.q = m->proj; sa.gate = L.has_gate ? m->proj : nullptr;
-		sa.ldq = (int) m->proj_ld; sa.q_off = L.off_lq; sa.g_off = L.off_lg;
+		sa.ldq = (int) m->proj_ld; sa.q_off = L.off_lq; sa.ldg = (int) m->proj_ld; sa.g_off = L.off_lg;
 		sa.kc = L.kc; sa.vc = L.vc; sa.ring = L.ring;
 		sa.H = H; sa.G = G; sa.d = d; sa.dv = dv;
 		sa.window = L.L.window > 0 ? L.L.window : 0x7fffffff;
@@ -382,21 +364,15 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		sa.step = m->d_step; sa.out = m->att;
 		sa.n_splits = n <= 4 ? m->max_splits : 1;
 		sa.part_o = m->part_o; sa.part_ml = m->part_ml;
-		const size_t asm_ = swa_smem_bytes(H, d, dv);
-		if (m->precision == XALM_PRECISION_F32) swa_attn_kernel<float><<<dim3(n, sa.n_splits), 256, asm_, s>>>(sa);
-		else swa_attn_kernel<__nv_bfloat16><<<dim3(n, sa.n_splits), 256, asm_, s>>>(sa);
-		NB_LAUNCH_CHECK("swa_attn");
-		if (sa.n_splits > 1) {
-			swa_merge_kernel<<<n, 256, 0, s>>>(sa);
-			NB_LAUNCH_CHECK("swa_merge");
-		}
+		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s));
+		*nl += sa.n_splits > 1 ? 2 : 1;
 		Hgrn2Args ha = {};
 		ha.proj = m->proj; ha.ld = (int) m->proj_ld; ha.q_off = L.off_rq; ha.f_off = L.off_rf; ha.v_off = L.off_rv;
 		ha.H = Hr; ha.d = dr; ha.dv = dvr;
 		ha.f_bias = L.fb; ha.lower = L.lower; ha.norm_w = L.rnorm; ha.eps = m->eps;
 		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro;
-		hgrn2_kernel<<<Hr, std::min(1024, (dvr + 31) / 32 * 32), hgrn2_smem_bytes(dr, dvr), s>>>(ha);
-		NB_LAUNCH_CHECK("hgrn2");
+		XALM_TRY(launch_hgrn2(ha, s));
+		(*nl)++;
 		RowsEpi est;
 		est.kind = EPI_STORE; est.out = m->ol; est.ldo = W;
 		XALM_TRY(rows_product(m, m->att, H * dv, L.w_lo, &L.m_lo, n, W, H * dv, est, nl));
@@ -406,23 +382,22 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		NB_LAUNCH_CHECK("dual_norm_hc");
 		// ---- feed-forward ----
 		if (L.has_mlp) {
-			hc_norm_kernel<<<n, rt, norm_smem, s>>>(m->xs, S, sstride, L.hc_in[1], L.norm2, 1, m->eps, W, m->h, nullptr);
-			NB_LAUNCH_CHECK("hc_norm");
+			XALM_TRY(launch_hc_norm(m->xs, S, sstride, L.hc_in[1], L.norm2, 1, m->eps, W, m->h, nullptr, n, s));
+			(*nl)++;
 			RowsEpi eg;
 			eg.kind = EPI_GLU; eg.out = m->y; eg.ldo = L.ff; eg.limit = L.limit;
 			XALM_TRY(rows_product(m, m->h, W, L.w_gu, &L.m_gu, n, 2 * L.ff, W, eg, nl));
 			XALM_TRY(rows_product(m, m->y, L.ff, L.w_down, &L.m_down, n, W, L.ff, hc_epi(m, L, 1), nl));
 		}
 		if (m->keep_layers) {
-			hc_norm_kernel<<<n, rt, norm_smem, s>>>(m->xs, S, sstride, nullptr, m->final_norm, 1, m->eps, W, nullptr,
-			                                        m->layer_sums + li * (size_t) m->chunk * W);
-			NB_LAUNCH_CHECK("layer sum");
+			XALM_TRY(launch_hc_norm(m->xs, S, sstride, nullptr, m->final_norm, 1, m->eps, W, nullptr, m->layer_sums + li * (size_t) m->chunk * W, n, s));
+			(*nl)++;
 		}
 	}
 	if (want) {
 		const int rows = want == 2 ? n : 1, first = want == 2 ? 0 : n - 1;
-		hc_norm_kernel<<<rows, rt, norm_smem, s>>>(m->xs + (size_t) first * W, S, sstride, nullptr, m->final_norm, 1, m->eps, W, m->h, nullptr);
-		NB_LAUNCH_CHECK("final norm");
+		XALM_TRY(launch_hc_norm(m->xs + (size_t) first * W, S, sstride, nullptr, m->final_norm, 1, m->eps, W, m->h, nullptr, rows, s));
+		(*nl)++;
 		RowsEpi eh;
 		eh.kind = EPI_STORE; eh.out = m->logits; eh.ldo = m->vocab;
 		XALM_TRY(rows_product(m, m->h, W, m->w_head, &m->m_head, rows, m->vocab, W, eh, nl));
@@ -535,18 +510,19 @@ extern const ModelFamily nabalix_family;
 
 int nb_create(const char* json, int device, int max_tokens, int precision, Nb** out) {
 	if (max_tokens <= 0) return set_error(XALM_ERR_INVALID, "max_tokens must be positive");
-	int ndev = 0;
-	XALM_CUDA_CHECK(cudaGetDeviceCount(&ndev));
-	if (device < 0 || device >= ndev) return set_error(XALM_ERR_CUDA, "device %d not available (%d devices)", device, ndev);
 	Nb* m = new Nb();
 	m->head.family = &nabalix_family;
 	m->device = device;
 	m->precision = precision;
 	m->max_tokens = max_tokens;
-	const int rc = parse_config(m, json);
+	const int rc = parse_config(m, json); // before the device is touched: a bad config is reported as such on any machine
 	if (rc != XALM_OK) { delete m; return rc; }
-	XALM_CUDA_CHECK(cudaSetDevice(device));
-	cudaError_t e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking);
+	int ndev = 0;
+	cudaError_t e = cudaGetDeviceCount(&ndev);
+	if (e != cudaSuccess) { delete m; return set_error(XALM_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(e)); }
+	if (device < 0 || device >= ndev) { delete m; return set_error(XALM_ERR_CUDA, "device %d not available (%d devices)", device, ndev); }
+	e = cudaSetDevice(device);
+	if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking);
 	if (e != cudaSuccess) { delete m; return set_error(XALM_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e)); }
 	m->stream = m->own_stream;
 	*out = m;
@@ -662,13 +638,10 @@ int nb_finalize(Nb* m) {
 		const size_t asm_ = swa_smem_bytes(H, d, dv), hsm = hgrn2_smem_bytes(dr, dvr);
 		if (asm_ > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: attention heads need %zu bytes of shared memory", li, asm_);
 		if (hsm > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: recurrence state needs %zu bytes of shared memory", li, hsm);
-		if (asm_ > 48 * 1024) {
-			XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-			XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-		}
-		if (hsm > 48 * 1024) XALM_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_TRY(swa_prepare(H, d, dv));
+		XALM_TRY(hgrn2_prepare(dr, dvr));
 	}
-	if ((size_t) (W + 33) * 4 > 48 * 1024) XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+	XALM_TRY(hc_norm_prepare(W));
 	m->proj_ld = (max_proj + 3) / 4 * 4;
 	const size_t C = (size_t) m->chunk;
 	m->max_splits = std::max(1, std::min(32, (max_ring + 4 * SWA_KB - 1) / (4 * SWA_KB)));
