@@ -381,6 +381,119 @@ def run_perplexity_workload(args):
     model.close()
 
 
+# ---- --workload families: the config.json family beside the closest .xalm model at equal size -----------------------------------
+FAMILY_SIZES = {   # layer shapes of real model classes; depth cut to keep the run short (throughput per layer is what is compared)
+    "w1024": dict(width=1024, ff=4096, heads=8, kv_heads=2, head_dim=128, window=512, r_heads=4, r_dim=64, r_vdim=128, layers=4, vocab=32000),
+    "w2048": dict(width=2048, ff=8192, heads=16, kv_heads=4, head_dim=128, window=1024, r_heads=8, r_dim=64, r_vdim=128, layers=4, vocab=32000),
+    "w4096": dict(width=4096, ff=14336, heads=32, kv_heads=8, head_dim=128, window=2048, r_heads=8, r_dim=128, r_vdim=128, layers=2, vocab=32000),
+}
+
+
+def nabalix_config(z: dict, streams: int = 2) -> dict:
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
+            "softcap": 30.0, "mask": {"size": z["window"]}}
+    right = {"heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"]}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}}
+    return {"architecture": "Nabalix", "vocab": z["vocab"], "width": z["width"], "streams": streams, "norm": {"eps": 1e-5},
+            "layers": [layer] * z["layers"]}
+
+
+def build_nabalix(z: dict, seed: int, max_tokens: int, stream):
+    """Random bf16 weights, uploaded tensor by tensor as the backend names them."""
+    import ctypes as C
+    import json
+    from xalm_b200 import capi, safetensors_io as ST, types as T
+    from xalm_b200.model import Model
+    m = Model._from_json_text(json.dumps(nabalix_config(z)), {})
+    L = capi.lib()
+    h = C.c_void_p()
+    capi.check(L.xalm_cuda_create_json(m.config["json"].encode(), 0, max_tokens, capi.PRECISION_BF16, C.byref(h)))
+    m._h = h
+    capi.check(L.xalm_cuda_set_stream(h, C.c_void_p(stream)))
+    rng = np.random.default_rng(seed)
+    for name, shape in m.expected_tensors().items():
+        leaf = name.split(".")[-1]
+        if len(shape) == 2 and leaf not in ("talk", "mix"):
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32(1.0 / np.sqrt(shape[1]))
+        elif leaf in ("talk", "mix"):
+            a = np.eye(shape[0], dtype=np.float32) + 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        elif leaf in ("norm1", "norm2") or name == "final.norm":
+            a = 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        elif leaf in ("r1", "r2", "lower"):
+            a = rng.uniform(0.05, 0.9, shape).astype(np.float32)
+        else:
+            a = 1.0 + 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        m.upload(name, T.BF16, shape, ST.f32_to_bf16_bits(a).view(np.uint8).reshape(-1))
+    capi.check(L.xalm_cuda_finalize(h))
+    m.config["vocab_size"] = z["vocab"]
+    return m
+
+
+def run_family_workload(args):
+    """Prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes (bf16 weights, random),
+    device-timed with CUDA events on the launching stream.  One JSON line; `value` is the Nabalix decode rate at the first size."""
+    import torch
+    from xalm_b200 import capi, synth, types as T, xalm_file as X
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the backend has no CPU fallback")
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    n_tok, ctx = args.tokens, args.tokens + args.steps + args.warmup + 8
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+    rows = {}
+    rng = np.random.default_rng(args.seed)
+    with ClockSampler(0) as clocks, torch.cuda.stream(stream):
+        for size in args.sizes.split(","):
+            z = FAMILY_SIZES[size]
+            toks = rng.integers(0, z["vocab"], n_tok + args.steps + args.warmup).astype(np.int32)
+            llama_full = synth.model_config("tiny", dim=z["width"], hidden_dim=z["ff"], head_dim=z["head_dim"], n_layers=z["layers"], n_heads=z["heads"],
+                                            n_kv_heads=z["kv_heads"], vocab_size=z["vocab"], max_seq_len=ctx, rope_theta=10000.0, rotary_dim=z["head_dim"])
+            llama_cfg = X.parse_config(synth.metadata_strings(llama_full), ctx)
+            for fam in ("nabalix", "llama"):
+                if fam == "nabalix":
+                    m = build_nabalix(z, args.seed, ctx, stream.cuda_stream)
+                else:
+                    m, _ = build_model_streaming(llama_full, llama_cfg, T.BF16, args.seed, False, stream=stream.cuda_stream)
+                    capi.tune("prefill_split", 1)        # plain fp16 operands, the counterpart of the one-plane path
+                ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+                pre = []
+                for it in range(3 + 3):                   # prompts of n_tok tokens from position 0: 3 warm-up, 3 timed
+                    if fam == "nabalix":
+                        m.release()
+                    flush.fill_(it)
+                    ev[0].record(stream)
+                    m.prefill_async(toks[:n_tok], 0, 1)
+                    ev[1].record(stream)
+                    stream.synchronize()
+                    if it >= 3:
+                        pre.append(ev[0].elapsed_time(ev[1]))
+                launches_prefill = m.last_launch_count()
+                dec = []
+                for i in range(args.warmup + args.steps):  # one-token steps continuing that prompt
+                    flush.fill_(i)
+                    ev[0].record(stream)
+                    m.forward_async(int(toks[n_tok + i]), n_tok + i, capi.OUTPUT_LOGITS)
+                    ev[1].record(stream)
+                    stream.synchronize()
+                    if i >= args.warmup:
+                        dec.append(ev[0].elapsed_time(ev[1]))
+                rows.setdefault(size, {})[fam] = {
+                    "prefill_tok_s": round(n_tok / (float(np.median(pre)) * 1e-3), 1), "prefill_ms": round(float(np.median(pre)), 3),
+                    "decode_tok_s": round(1e3 / float(np.mean(dec)), 1), "decode_ms": round(float(np.mean(dec)), 4),
+                    "decode_bytes": m.active_bytes(n_tok + args.steps // 2), "launches_prefill": launches_prefill, "launches_decode": m.last_launch_count()}
+                r = rows[size][fam]
+                r["decode_roofline"] = round(r["decode_bytes"] / (r["decode_ms"] * 1e-3) / 1e9 / measured_peak_gbs()[0], 3)
+                m.close()
+                capi.tune("prefill_split", 3)
+    first = args.sizes.split(",")[0]
+    print(json.dumps({"metric": "decode_tokens_per_s_nabalix_vs_llama", "value": rows[first]["nabalix"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": rows[first]["nabalix"]["decode_ms"], "higher_is_better": True,
+                      "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "families", "prompt_tokens": n_tok, "sizes": {s: FAMILY_SIZES[s] for s in rows},
+                                 "l2": "a 192 MB buffer is written between timed iterations", "peak_gbs": measured_peak_gbs()[0]},
+                      "families": rows, "clocks": clocks.summary()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -399,8 +512,10 @@ def main():
     ap.add_argument("--past-window", action="store_true",
                     help="also time steps at positions >= ctx: the KV ring is full (kv_len = ctx), 2 attention sinks active (infer.cpp:608-613)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the perplexity-mode summary appended to the decode line at N=1")
-    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity"],
-                    help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input")
+    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families"],
+                    help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input; "
+                         "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes")
+    ap.add_argument("--sizes", default="w1024,w2048,w4096", help="families workload: which of " + ",".join(FAMILY_SIZES))
     ap.add_argument("--tokens", type=int, default=4096, help="perplexity workload: tokens per step")
     ap.add_argument("--split", type=int, default=0, help="perplexity workload: operand precision (0 = library default 3; 1 = plain fp16)")
     args = ap.parse_args()
@@ -408,6 +523,13 @@ def main():
 
     if args.workload == "perplexity":
         run_perplexity_workload(args)
+        return
+    if args.workload == "families":
+        if args.steps == 256:
+            args.steps = 64
+        if args.tokens == 4096:
+            args.tokens = 2048
+        run_family_workload(args)
         return
     if args.impl == "reference":
         run_reference(args)

@@ -161,7 +161,9 @@ def test_clamped_glu_op(T, bf16):
 LAYER_A = dict(H=4, G=2, d=8, dv=12, window=9, softcap=6.0, Hr=2, dr=8, dvr=6, ff=56, limit=1.0)
 LAYER_B = dict(H=3, G=3, d=16, dv=8, window=21, softcap=4.0, Hr=1, dr=4, dvr=24, ff=None)
 LAYER_C = dict(H=2, G=1, d=4, dv=4, window=5, scale=0.9, softcap=2.0, Hr=3, dr=5, dvr=7, ff=40, limit=3.0)
+LAYER_T = dict(H=4, G=2, d=8, dv=16, window=19, softcap=5.0, Hr=2, dr=6, dvr=32, ff=128, limit=1.5)   # every product a whole number of 64-wide K tiles
 CONFIGS = {
+    "k64_tiles": O.make_config(vocab=68, width=64, streams=2, layers=[LAYER_T, dict(LAYER_T, ff=None), LAYER_T]),
     "mixed3": O.make_config(vocab=67, width=48, streams=2, layers=[LAYER_A, LAYER_B, LAYER_C]),
     "one_stream": O.make_config(vocab=31, width=40, streams=1, layers=[LAYER_C, LAYER_A]),
     "three_streams": O.make_config(vocab=90, width=72, streams=3, layers=[LAYER_B, LAYER_A], eps=1e-3),
@@ -218,6 +220,32 @@ def test_portions_and_token_by_token(case, chunk, cuts):
     m = on_gpu(cfg, W, capi.PRECISION_F32, chunk=chunk)
     close(step_all(m, tokens, cuts), logits, F32_TOL)
     m.close()
+
+
+def test_tensor_core_passes_match_the_fp32_kernels():
+    """16-bit mode: passes of 32 tokens or more run their products on the tcgen05 GEMM (where every K is a multiple of 64), shorter
+    ones on the fp32 FMA kernels; both agree with the oracle, with one activation plane and with hi + lo planes."""
+    cfg = CONFIGS["k64_tiles"]
+    W = O.random_weights(cfg, seed=9)
+    tokens = np.random.default_rng(4).integers(0, cfg["vocab"], 150).tolist()
+    logits, _ = O.forward(cfg, W, tokens)
+    for tc, tol in ((1, BF16_TOL), (2, BF16_TOL), (0, BF16_TOL)):
+        capi.tune("seq_tc", tc)
+        try:
+            m = on_gpu(cfg, W, capi.PRECISION_BF16, chunk=64)
+        finally:
+            capi.tune("seq_tc", 1)
+        launches = []
+        for cuts in ([150], [40, 33, 5, 64, 8]):
+            close(step_all(m, tokens, cuts), logits, tol)
+            launches.append(m.last_launch_count())
+            m.release()
+        m.close()
+        if tc == 0:
+            base = launches
+        else:
+            tc_launches = launches
+    assert tc_launches[1] != base[1] or tc_launches[0] != base[0]      # the tensor-core path really ran (it launches pack + GEMM + epilogue)
 
 
 def test_forward_steps_use_the_graph_and_match(case):

@@ -66,7 +66,9 @@ static std::map<std::string, int>& tuning() {
 	                          // activations, 3 = hi+lo on activations, weights and attention operands (default: logits within ~1e-3 of the decode path)
 	    {"seq_graph", 1},     // config.json families: replay a captured CUDA graph for one-token steps
 	    {"seq_chunk", 256},   // config.json families: most positions one pass of a prompt covers (longer steps are cut)
-	    {"seq_tc", 1},        // config.json families, 16-bit serving mode: batched matrix products on the tcgen05 path where the shapes allow
+	    {"seq_tc", 1},        // config.json families, 16-bit serving mode: passes of many tokens run their matrix products on the tcgen05 GEMM where the
+	                          // shapes allow; 1 = activations as one fp16 plane, 2 = hi + lo planes (fp32-grade), 0 = fp32 FMA kernels only
+	    {"seq_tc_min", 32},   // fewest tokens in a pass for that path
 	};
 	return t;
 }

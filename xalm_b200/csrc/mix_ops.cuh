@@ -234,6 +234,19 @@ __global__ void __launch_bounds__(256) rows_gemm_kernel(const float* __restrict_
 	}
 }
 
+// ---- the epilogues alone, on a product that another kernel left in memory (the tensor-core GEMM stores plain fp32 rows) --------------
+static __global__ void rows_epilogue_kernel(const float* __restrict__ src, int lds, int T, int N, RowsEpi e) {
+	const int step = e.kind == EPI_GLU ? 2 : 1, per_row = (N + step - 1) / step;
+	const size_t total = (size_t) T * per_row;
+	for (size_t i = blockIdx.x * (size_t) blockDim.x + threadIdx.x; i < total; i += (size_t) gridDim.x * blockDim.x) {
+		const int row = (int) (i / per_row), col = (int) (i % per_row) * step;
+		const float* p = src + (size_t) row * lds + col;
+		if (step == 2) {
+			if (col + 1 < N) epi_apply(e, row, col, N, p[0], p[1]);
+		} else epi_apply(e, row, col, N, p[0], 0.f);
+	}
+}
+
 // ---- the same for T <= TB tokens: a warp per pair of output columns -------------------------------------------------------------
 template <typename WT, int TB>
 __global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
@@ -590,6 +603,12 @@ static inline int hgrn2_prepare(int d, int dv) {
 		raised = true;
 	}
 	return XALM_OK;
+}
+
+static inline int launch_rows_epilogue(const float* src, int lds, int T, int N, const RowsEpi& e, cudaStream_t s) {
+	const size_t total = (size_t) T * (e.kind == EPI_GLU ? (N + 1) / 2 : N);
+	rows_epilogue_kernel<<<(int) std::min<size_t>((total + 255) / 256, 148 * 16), 256, 0, s>>>(src, lds, T, N, e);
+	return launch_check("row epilogue");
 }
 
 static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, const float* a, const float* w, int one_plus, float eps, int width, float* h,

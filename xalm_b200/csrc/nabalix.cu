@@ -77,6 +77,7 @@ struct Layer {
 	void* w_gu = nullptr;   // (2 ff) x width, gate and up rows interleaved
 	void* w_down = nullptr; // width x ff
 	WMat m_in, m_lo, m_ro, m_gu, m_down; // the same buffers as the tensor-core path's operand descriptors
+	TcWeight t_in, t_lo, t_ro, t_gu, t_down; // resident fp16 operand tiles for passes of many tokens (16-bit mode)
 	int n_in = 0, n_plain = 0, off_lq = 0, off_lg = 0, off_rq = 0, off_rf = 0, off_rv = 0;
 	bool has_gate = false;
 	float *norm1 = nullptr, *norm2 = nullptr, *r1 = nullptr, *r2 = nullptr, *talk = nullptr, *fb = nullptr, *lower = nullptr, *rnorm = nullptr;
@@ -106,6 +107,10 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	std::vector<void*> allocs;
 	void *embed = nullptr, *w_head = nullptr;
 	WMat m_head;
+	TcWeight t_head;
+	uint8_t *a_hi = nullptr, *a_lo = nullptr; // activation operand planes of the tensor-core path
+	float* tc_out = nullptr;                  // its plain fp32 product, when an epilogue follows
+	int tc_min_rows = 32;
 	float* final_norm = nullptr;
 	// activations of one pass
 	int chunk = 256;
@@ -121,7 +126,7 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	int pos = 0; // tokens the running sequence holds
 	int last_launches = 0;
 	bool use_tc = false;
-	long long weight_bytes = 0;
+	long long weight_bytes = 0, weight_bytes_tc = 0;
 };
 
 namespace xalm {
@@ -303,9 +308,20 @@ int upload_rows(Nb* m, const std::vector<const HostTensor*>& parts, int K, bool 
 	return XALM_OK;
 }
 
-// ---- row products: fp32 FMA kernels (mix_ops.cuh) -----------------------------------------------------------------------------
-int rows_product(Nb* m, const float* A, int lda, const void* W, const WMat* wm, int T, int N, int K, const RowsEpi& e, int* nl) {
-	(void) wm;
+// ---- row products -------------------------------------------------------------------------------------------------------------
+// Passes of few tokens and the fp32 mode: the fp32 FMA kernels of mix_ops.cuh with the epilogue fused.  Passes of tc_min_rows tokens
+// or more in the 16-bit mode: the tcgen05 GEMM of prefill.cu on the weight's resident fp16 tiles (activations packed to fp16, one
+// plane, or hi + lo with "seq_tc" = 2), fp32 accumulation, then the same epilogue as an elementwise kernel.
+int rows_product(Nb* m, const float* A, int lda, const void* W, const TcWeight* tw, int T, int N, int K, const RowsEpi& e, int* nl) {
+	if (m->use_tc && tw && tw->hi && T >= m->tc_min_rows && lda == K) {
+		if (e.kind == EPI_STORE && e.ldo % 4 == 0) {
+			*nl += 2;
+			return tc_gemm(*tw, A, T, e.out, e.ldo, m->a_hi, m->a_lo, m->stream);
+		}
+		*nl += 3;
+		XALM_TRY(tc_gemm(*tw, A, T, m->tc_out, N, m->a_hi, m->a_lo, m->stream));
+		return launch_rows_epilogue(m->tc_out, N, T, N, e, m->stream);
+	}
 	(*nl)++;
 	return launch_rows(A, lda, W, m->w_bf16, T, N, K, e, m->stream);
 }
@@ -352,7 +368,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		ein.n_plain = L.n_plain; ein.kdim = G * d; ein.vdim = G * dv; ein.ring = L.ring;
 		ein.cache_f32 = m->precision == XALM_PRECISION_F32;
 		ein.kc = L.kc; ein.vc = L.vc; ein.step = m->d_step;
-		XALM_TRY(rows_product(m, m->h, W, L.w_in, &L.m_in, n, L.n_in, W, ein, nl));
+		XALM_TRY(rows_product(m, m->h, W, L.w_in, &L.t_in, n, L.n_in, W, ein, nl));
 		SwaArgs sa = {};
 		sa.q = m->proj; sa.gate = L.has_gate ? m->proj : nullptr;
 		sa.ldq = (int) m->proj_ld; sa.q_off = L.off_lq; sa.ldg = (int) m->proj_ld; sa.g_off = L.off_lg;
@@ -375,9 +391,9 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		(*nl)++;
 		RowsEpi est;
 		est.kind = EPI_STORE; est.out = m->ol; est.ldo = W;
-		XALM_TRY(rows_product(m, m->att, H * dv, L.w_lo, &L.m_lo, n, W, H * dv, est, nl));
+		XALM_TRY(rows_product(m, m->att, H * dv, L.w_lo, &L.t_lo, n, W, H * dv, est, nl));
 		est.out = m->orr;
-		XALM_TRY(rows_product(m, m->ro, Hr * dvr, L.w_ro, &L.m_ro, n, W, Hr * dvr, est, nl));
+		XALM_TRY(rows_product(m, m->ro, Hr * dvr, L.w_ro, &L.t_ro, n, W, Hr * dvr, est, nl));
 		dual_norm_hc_kernel<<<n, rt, 33 * 4, s>>>(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0));
 		NB_LAUNCH_CHECK("dual_norm_hc");
 		// ---- feed-forward ----
@@ -386,8 +402,8 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 			(*nl)++;
 			RowsEpi eg;
 			eg.kind = EPI_GLU; eg.out = m->y; eg.ldo = L.ff; eg.limit = L.limit;
-			XALM_TRY(rows_product(m, m->h, W, L.w_gu, &L.m_gu, n, 2 * L.ff, W, eg, nl));
-			XALM_TRY(rows_product(m, m->y, L.ff, L.w_down, &L.m_down, n, W, L.ff, hc_epi(m, L, 1), nl));
+			XALM_TRY(rows_product(m, m->h, W, L.w_gu, &L.t_gu, n, 2 * L.ff, W, eg, nl));
+			XALM_TRY(rows_product(m, m->y, L.ff, L.w_down, &L.t_down, n, W, L.ff, hc_epi(m, L, 1), nl));
 		}
 		if (m->keep_layers) {
 			XALM_TRY(launch_hc_norm(m->xs, S, sstride, nullptr, m->final_norm, 1, m->eps, W, nullptr, m->layer_sums + li * (size_t) m->chunk * W, n, s));
@@ -400,7 +416,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		(*nl)++;
 		RowsEpi eh;
 		eh.kind = EPI_STORE; eh.out = m->logits; eh.ldo = m->vocab;
-		XALM_TRY(rows_product(m, m->h, W, m->w_head, &m->m_head, rows, m->vocab, W, eh, nl));
+		XALM_TRY(rows_product(m, m->h, W, m->w_head, &m->t_head, rows, m->vocab, W, eh, nl));
 	}
 	return XALM_OK;
 }
@@ -501,6 +517,9 @@ void nb_destroy(Nb* m) {
 	for (int i = 0; i < 2; i++)
 		if (m->graph[i]) cudaGraphExecDestroy(m->graph[i]);
 	for (void* p : m->allocs) cudaFree(p);
+	for (Layer& L : m->layers)
+		for (TcWeight* t : {&L.t_in, &L.t_lo, &L.t_ro, &L.t_gu, &L.t_down}) tc_weight_free(t);
+	tc_weight_free(&m->t_head);
 	if (m->h_logits) cudaFreeHost(m->h_logits);
 	if (m->own_stream) cudaStreamDestroy(m->own_stream);
 	delete m;
@@ -642,6 +661,36 @@ int nb_finalize(Nb* m) {
 		XALM_TRY(hgrn2_prepare(dr, dvr));
 	}
 	XALM_TRY(hc_norm_prepare(W));
+	// tensor-core operands: every matrix whose shape the GEMM takes keeps its fp16 tiles beside the bf16 rows the one-token steps stream
+	m->use_tc = m->w_bf16 && tune("seq_tc") > 0;
+	m->tc_min_rows = std::max(1, tune("seq_tc_min"));
+	size_t a_bytes = 0, tc_cols = 4;
+	if (m->use_tc) {
+		auto build = [&](const WMat& wm, TcWeight* t) -> int {
+			if (!tc_shape_ok(wm.rows, wm.n, wm.rows)) return XALM_OK; // this one stays on the fp32 kernels
+			XALM_TRY(tc_weight_build(wm, 1, t, m->stream));
+			a_bytes = std::max(a_bytes, tc_a_plane_bytes(m->chunk, wm.n));
+			tc_cols = std::max(tc_cols, (size_t) wm.rows);
+			m->weight_bytes_tc += (long long) t->NT * t->KT * 256 * 64 * 2;
+			return XALM_OK;
+		};
+		for (Layer& L : m->layers) {
+			XALM_TRY(build(L.m_in, &L.t_in));
+			XALM_TRY(build(L.m_lo, &L.t_lo));
+			XALM_TRY(build(L.m_ro, &L.t_ro));
+			if (L.has_mlp) {
+				XALM_TRY(build(L.m_gu, &L.t_gu));
+				XALM_TRY(build(L.m_down, &L.t_down));
+			}
+		}
+		XALM_TRY(build(m->m_head, &m->t_head));
+		if (a_bytes) {
+			XALM_TRY(dev_alloc(m, &m->a_hi, a_bytes, true));
+			if (tune("seq_tc") >= 2) XALM_TRY(dev_alloc(m, &m->a_lo, a_bytes, true));
+			XALM_TRY(dev_alloc(m, &m->tc_out, (size_t) m->chunk * tc_cols));
+		} else m->use_tc = false;
+		XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
+	}
 	m->proj_ld = (max_proj + 3) / 4 * 4;
 	const size_t C = (size_t) m->chunk;
 	m->max_splits = std::max(1, std::min(32, (max_ring + 4 * SWA_KB - 1) / (4 * SWA_KB)));

@@ -1759,4 +1759,34 @@ int prefill_bench_gemm(int T, int N, int K, int split, int iters, float* ms_per_
 	return XALM_OK;
 }
 
+// ---- resident operands (prefill.h) ----------------------------------------------------------------------------------------------
+int tc_weight_build(const WMat& w, int planes, TcWeight* out, cudaStream_t s) {
+	const int K = w.n, N = w.rows;
+	if (K % GB_K) return set_error(XALM_ERR_INVALID, "tc_weight_build: K = %d is not a multiple of %d", K, GB_K);
+	*out = TcWeight();
+	out->N = N; out->K = K; out->NT = cdiv(N, GB_N); out->KT = K / GB_K;
+	const size_t bytes = (size_t) out->NT * out->KT * B_TILE_BYTES;
+	XALM_CUDA_CHECK(cudaMalloc((void**) &out->hi, bytes));
+	if (planes >= 2) XALM_CUDA_CHECK(cudaMalloc((void**) &out->lo, bytes));
+	return launch_dequant_tiles(w, false, 0, N, K, out->NT, out->KT, out->hi, out->lo, s);
+}
+void tc_weight_free(TcWeight* w) {
+	if (!w) return;
+	if (w->hi) cudaFree(w->hi);
+	if (w->lo) cudaFree(w->lo);
+	*w = TcWeight();
+}
+size_t tc_a_plane_bytes(int T, int K) { return (size_t) cdiv(T, GB_M) * cdiv(K, GB_K) * A_TILE_BYTES; }
+
+int tc_gemm(const TcWeight& w, const float* a_dev, int T, float* out_dev, int ldo, uint8_t* a_hi, uint8_t* a_lo, cudaStream_t s) {
+	if (!tc_shape_ok(w.N, w.K, ldo) || T <= 0) return set_error(XALM_ERR_INVALID, "tc_gemm: shape (%d x %d) . (%d x %d)^T, ldo %d", T, w.K, w.N, w.K, ldo);
+	const int MT = cdiv(T, GB_M);
+	ATiles at{a_hi, a_lo, w.KT};
+	pack_a_kernel<<<std::min(cdiv(T * (w.K / 8), 256), sm_count() * 8), 256, 0, s>>>(a_dev, T, w.K, at);
+	GemmArgs g = {};
+	g.a_hi = a_hi; g.a_lo = a_lo; g.b = w.hi; g.b_lo = w.lo;
+	g.MT = MT; g.NT = w.NT; g.KT = w.KT; g.M = T; g.N = w.N; g.epi = GEPI_STORE; g.out = out_dev; g.ldo = ldo;
+	return launch_gemm(g, a_lo ? 2 : 1, w.lo ? 2 : 1, s);
+}
+
 } // namespace xalm

@@ -53,4 +53,20 @@ int prefill_gemm_dev(const WMat& w, const float* a_dev, int T, float* out_dev, i
 // Times `iters` launches of the GEMM kernel alone (operands resident, dequantised tiles prepared once).
 int prefill_bench_gemm(int T, int N, int K, int split, int iters, float* ms_per_launch);
 
+// ---- resident operands: the GEMM above for callers that keep a weight's tensor-core tiles for the life of the model ------------
+// (model families whose passes are built from plain row products: out(T,N) = a(T,K) . W(N,K)^T, fp32 in and out).
+struct TcWeight {
+	uint8_t* hi = nullptr; // fp16 B tiles, 256 rows x 64 K-elements each
+	uint8_t* lo = nullptr; // rounding residuals (two weight planes), or NULL
+	int N = 0, K = 0, NT = 0, KT = 0;
+};
+// Shapes the kernel takes: whole 64-element K tiles, 16-byte rows of fp32 output.
+inline bool tc_shape_ok(int N, int K, int ldo) { return K % 64 == 0 && N % 4 == 0 && ldo % 4 == 0; }
+int tc_weight_build(const WMat& w, int planes, TcWeight* out, cudaStream_t s); // allocates out->hi (/lo); W in its decode layout
+void tc_weight_free(TcWeight* w);
+size_t tc_a_plane_bytes(int T, int K); // one operand plane of T x K activations
+// a_hi / a_lo: caller-owned planes of tc_a_plane_bytes(T, K) bytes (a_lo NULL: one fp16 plane; else hi + lo = fp32-grade activations).
+// Two launches (pack, GEMM) on stream s; nothing is synchronised.
+int tc_gemm(const TcWeight& w, const float* a_dev, int T, float* out_dev, int ldo, uint8_t* a_hi, uint8_t* a_lo, cudaStream_t s);
+
 } // namespace xalm
