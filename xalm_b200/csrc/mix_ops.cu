@@ -68,7 +68,7 @@ int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const
 	if (ring < need) return set_error(XALM_ERR_INVALID, "swa_attention: a ring of %d slots cannot hold %lld live positions", ring, need);
 	if (!r1 != !r2) return set_error(XALM_ERR_INVALID, "swa_attention: r1 and r2 come together");
 	const size_t smem = swa_smem_bytes(H, d, dv);
-	if (smem > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "swa_attention: heads need %zu bytes of shared memory", smem);
+	if (!swa_pick_tq(H, G, d, dv, T) && smem > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "swa_attention: heads need %zu bytes of shared memory", smem);
 	Pool pool;
 	// the ring as the cache manager leaves it: position p lives in slot p % ring, older positions are overwritten
 	const size_t esz = cache_bf16 ? 2 : 4;
@@ -100,6 +100,7 @@ int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const
 	float* d_out = pool.raw<float>((size_t) T * H * dv);
 	a.out = d_out;
 	a.n_splits = n_splits;
+	a.part_cap = T * n_splits;
 	a.part_o = pool.raw<float>((size_t) T * n_splits * H * dv);
 	a.part_ml = pool.raw<float>((size_t) T * n_splits * H * 2);
 	if (!a.q || !a.kc || !a.vc || !a.step || !d_out || !a.part_o || !a.part_ml) return set_error(XALM_ERR_CUDA, "swa_attention: device allocation failed");
@@ -113,7 +114,7 @@ int xalm_cuda_hgrn2(float* out, float* state, const float* qz, const float* fz, 
                     const float* lower, const float* norm_w, float eps) {
 	if (!out || !state || !qz || !fz || !v || T <= 0 || H <= 0 || d <= 0 || dv <= 0) return set_error(XALM_ERR_INVALID, "hgrn2: bad argument");
 	const size_t smem = hgrn2_smem_bytes(d, dv);
-	if (smem > 200 * 1024 || dv > 1024) return set_error(XALM_ERR_UNSUPPORTED, "hgrn2: a head's state needs %zu bytes of shared memory", smem);
+	if (!hgrn2_cols_ok(d, dv, T) && (smem > 200 * 1024 || dv > 1024)) return set_error(XALM_ERR_UNSUPPORTED, "hgrn2: a head's state needs %zu bytes of shared memory", smem);
 	Pool pool;
 	const int ld = 2 * H * d + H * dv;
 	std::vector<float> proj((size_t) T * ld);
@@ -133,6 +134,7 @@ int xalm_cuda_hgrn2(float* out, float* state, const float* qz, const float* fz, 
 	a.step = pool.put(&st, 1);
 	float* d_out = pool.raw<float>((size_t) T * H * dv);
 	a.out = d_out;
+	a.max_rows = T;
 	if (!a.proj || !a.state || !a.step || !d_out) return set_error(XALM_ERR_CUDA, "hgrn2: device allocation failed");
 	XALM_TRY(launch_hgrn2(a, nullptr));
 	XALM_TRY(finish("hgrn2"));

@@ -22,6 +22,7 @@
 // Numerics: everything here is fp32 (expf / tanhf / log1pf, no fast-math); 16-bit storage appears only as weight and K/V-cache
 // element types.
 #pragma once
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
@@ -325,7 +326,9 @@ struct SwaArgs {
 	const float* talk; // (H, H) score_h <- sum_g talk[h, g] score_g; NULL: none
 	const SeqStep* step;
 	float* out;        // (T, H * dv)
-	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes
+	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes.  0: the launcher chooses (part_cap bounds it)
+	int part_cap;      // (row, split) pairs part_o / part_ml have room for (only read when n_splits == 0)
+	int tq;            // queries per CTA of the tiled kernel (set by the launcher)
 	float* part_o;     // (T, n_splits, H * dv)
 	float* part_ml;    // (T, n_splits, H, 2)
 };
@@ -458,6 +461,228 @@ static __global__ void swa_merge_kernel(SwaArgs a) {
 	}
 }
 
+// ---- the same attention, tiled: a CTA takes `tq` consecutive queries with ALL their heads (the score mixing needs every head's score
+// of a query-key pair) and walks the keys SWA_KB at a time ------------------------------------------------------------------------
+// Rows of the tile are (kv group g, head in group, query): row = g * Rg + hr * tq + q with Rg = rep * tq rounded up to 4, so that the
+// rows of one group are contiguous and share that group's K and V tile.  Per key block:
+//   for every group: K tile -> shared memory; raw scores = 4x4 register tiles of Q . K^T (both row-major, float4 along the channel;
+//                    a thread's 4 keys are 8 apart, which keeps the 16-byte loads of a quarter-warp on distinct banks);
+//                    scale, soft cap, distance bias -> Sc[key][row]
+//   mix heads (4 output heads per thread) and mask -> Pr[key][row];  online softmax, a warp per row
+//   for every group: V tile -> shared memory; O[row][:] = alpha O + P^T . V in 4x4 register tiles (float4 along rows and columns)
+// Keys can be split over blockIdx.y for short steps (swa_merge_kernel joins).  Everything is fp32; the cache element type only sets
+// how K and V are loaded.
+struct SwaTile {
+	int tq, Rg, R, dp, ldq, dvp, Hp;
+};
+__host__ __device__ inline SwaTile swa_tile_dims(int H, int G, int d, int dv, int tq) {
+	SwaTile t;
+	t.tq = tq;
+	t.Rg = ((H / G) * tq + 3) & ~3;
+	t.R = G * t.Rg;
+	t.dp = (d + 3) & ~3;
+	t.ldq = t.dp + 4;
+	t.dvp = (dv + 3) & ~3;
+	t.Hp = (H + 3) & ~3;
+	return t;
+}
+__host__ __device__ inline size_t swa_tile_smem_floats(int H, int G, int d, int dv, int tq) {
+	const SwaTile t = swa_tile_dims(H, G, d, dv, tq);
+	const size_t kv = (size_t) SWA_KB * (t.ldq > t.dvp ? t.ldq : t.dvp);
+	return (size_t) t.R * t.ldq + kv + 2 * (size_t) SWA_KB * t.R + (size_t) t.R * t.dvp + (size_t) H * t.Hp + 3 * (size_t) t.R;
+}
+
+template <typename CT>
+__global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
+	extern __shared__ __align__(16) float sm[];
+	const int H = a.H, G = a.G, d = a.d, dv = a.dv, rep = H / G, TQ = a.tq;
+	const SwaTile z = swa_tile_dims(H, G, d, dv, TQ);
+	const int Rg = z.Rg, R = z.R, dp = z.dp, ldq = z.ldq, dvp = z.dvp, Hp = z.Hp;
+	const int ldkv = ldq > dvp ? ldq : dvp;
+	float* Qs = sm;                          // R * ldq
+	float* KV = Qs + (size_t) R * ldq;       // SWA_KB * ldkv: one group's K tile, later its V tile
+	float* Sc = KV + (size_t) SWA_KB * ldkv; // SWA_KB * R raw scores
+	float* Pr = Sc + (size_t) SWA_KB * R;    // SWA_KB * R mixed scores, then probabilities
+	float* O = Pr + (size_t) SWA_KB * R;     // R * dvp
+	float* tkT = O + (size_t) R * dvp;       // H * Hp: tkT[g * Hp + h] = talk[h, g]
+	float* mrun = tkT + (size_t) H * Hp;     // R
+	float* lrun = mrun + R;                  // R
+	float* alpha = lrun + R;                 // R
+	const CT* kc = reinterpret_cast<const CT*>(a.kc);
+	const CT* vc = reinterpret_cast<const CT*>(a.vc);
+	const int tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
+	const int n = a.step->n, pos0 = a.step->pos0;
+	const int t0 = blockIdx.x * TQ, sp = blockIdx.y;
+	const int nq = min(TQ, n - t0);          // queries of this tile (<= 0: nothing to do)
+	if (nq <= 0) return;
+	const int i_lo = pos0 + t0, i_hi = i_lo + nq - 1;
+	const int j_first = a.window < 0x7fffffff ? max(0, i_lo - a.window + 1) : 0;
+	const int nk = i_hi - j_first + 1;
+	int per = (nk + a.n_splits - 1) / a.n_splits;
+	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
+	const int jb = j_first + sp * per, je = min(i_hi + 1, jb + per);
+
+	// ---- Q tile (zero rows where the tile has no head or no query), constants ----
+	for (int x = tid; x < R * (dp >> 2); x += nth) {
+		const int row = x / (dp >> 2), k4 = (x % (dp >> 2)) << 2;
+		const int g = row / Rg, rr = row % Rg, hr = rr / TQ, q = rr % TQ;
+		float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+		if (hr < rep && q < nq) {
+			const float* src = a.q + (size_t) (t0 + q) * a.ldq + a.q_off + (g * rep + hr) * d + k4;
+			v.x = src[0];
+			if (k4 + 1 < d) v.y = src[1];
+			if (k4 + 2 < d) v.z = src[2];
+			if (k4 + 3 < d) v.w = src[3];
+		}
+		*reinterpret_cast<float4*>(Qs + (size_t) row * ldq + k4) = v;
+	}
+	for (int x = tid; x < H * Hp; x += nth) {
+		const int g = x / Hp, h = x % Hp;
+		tkT[x] = h < H ? (a.talk ? a.talk[h * H + g] : (h == g ? 1.f : 0.f)) : 0.f;
+	}
+	for (int x = tid; x < R; x += nth) { mrun[x] = -INFINITY; lrun[x] = 0.f; alpha[x] = 0.f; }
+	for (int x = tid; x < R * dvp; x += nth) O[x] = 0.f;
+
+	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
+		const int nbk = min(SWA_KB, je - j0);
+		// ---- raw scores, one kv group at a time ----
+		for (int g = 0; g < G; g++) {
+			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
+			for (int x = tid; x < SWA_KB * dp; x += nth) {
+				const int jj = x / dp, k = x % dp;
+				KV[jj * ldkv + k] = (jj < nbk && k < d) ? ldf(kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + g * d + k) : 0.f;
+			}
+			__syncthreads();
+			for (int tile = tid; tile < (Rg >> 2) * 8; tile += nth) {
+				const int mt = tile >> 3, nt = tile & 7;
+				const float* qp = Qs + (size_t) (g * Rg + 4 * mt) * ldq;
+				const float* kp = KV + nt * ldkv;
+				float acc[4][4] = {};
+				for (int k = 0; k < dp; k += 4) {
+					float4 qv[4], kv[4];
+#pragma unroll
+					for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(qp + i * ldq + k);
+#pragma unroll
+					for (int u = 0; u < 4; u++) kv[u] = *reinterpret_cast<const float4*>(kp + u * 8 * ldkv + k);
+#pragma unroll
+					for (int i = 0; i < 4; i++)
+#pragma unroll
+						for (int u = 0; u < 4; u++) {
+							acc[i][u] = fmaf(qv[i].x, kv[u].x, acc[i][u]);
+							acc[i][u] = fmaf(qv[i].y, kv[u].y, acc[i][u]);
+							acc[i][u] = fmaf(qv[i].z, kv[u].z, acc[i][u]);
+							acc[i][u] = fmaf(qv[i].w, kv[u].w, acc[i][u]);
+						}
+				}
+#pragma unroll
+				for (int u = 0; u < 4; u++) {
+					const int jj = nt + 8 * u, j = j0 + jj;
+					float o4[4];
+#pragma unroll
+					for (int i = 0; i < 4; i++) {
+						const int rr = 4 * mt + i, hr = rr / TQ, q = rr % TQ;
+						float s = 0.f;
+						if (hr < rep && q < nq && jj < nbk) {
+							const int h = g * rep + hr;
+							s = acc[i][u] * a.scale;
+							if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+							if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) max(i_lo + q - j, 0));
+						}
+						o4[i] = s;
+					}
+					*reinterpret_cast<float4*>(Sc + (size_t) jj * R + g * Rg + 4 * mt) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+				}
+			}
+		}
+		__syncthreads();
+		// ---- mix the heads' scores (4 output heads per thread), mask ----
+		for (int x = tid; x < SWA_KB * TQ * (Hp >> 2); x += nth) {
+			const int hq = x % (Hp >> 2), rest = x / (Hp >> 2), q = rest % TQ, jj = rest / TQ;
+			float m4[4] = {0.f, 0.f, 0.f, 0.f};
+			const float* srow = Sc + (size_t) jj * R + q;
+			for (int g = 0; g < H; g++) {
+				const float s = srow[(g / rep) * Rg + (g % rep) * TQ];
+				const float4 w = *reinterpret_cast<const float4*>(tkT + g * Hp + 4 * hq);
+				m4[0] = fmaf(w.x, s, m4[0]); m4[1] = fmaf(w.y, s, m4[1]); m4[2] = fmaf(w.z, s, m4[2]); m4[3] = fmaf(w.w, s, m4[3]);
+			}
+			const int i = i_lo + q, j = j0 + jj;
+			const bool seen = q < nq && jj < nbk && j <= i && (a.window >= 0x7fffffff || i - j < a.window);
+#pragma unroll
+			for (int u = 0; u < 4; u++) {
+				const int h = 4 * hq + u;
+				if (h < H) Pr[(size_t) jj * R + (h / rep) * Rg + (h % rep) * TQ + q] = seen ? m4[u] : -INFINITY;
+			}
+		}
+		__syncthreads();
+		// ---- online softmax, a warp per (head, query) row; lane = key ----
+		for (int x = warp; x < H * TQ; x += nw) {
+			const int h = x / TQ, q = x % TQ, row = (h / rep) * Rg + (h % rep) * TQ + q;
+			const float s = Pr[(size_t) lane * R + row]; // SWA_KB == 32
+			const float bm = warp_max(s);
+			const float m_old = mrun[row], m_new = fmaxf(m_old, bm);
+			const float p = (m_new == -INFINITY) ? 0.f : expf(s - m_new);
+			const float ps = warp_sum(p);
+			Pr[(size_t) lane * R + row] = p;
+			if (lane == 0) {
+				const float al = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+				alpha[row] = al;
+				mrun[row] = m_new;
+				lrun[row] = lrun[row] * al + ps;
+			}
+		}
+		// ---- O <- alpha O + P^T V, one kv group at a time ----
+		for (int g = 0; g < G; g++) {
+			__syncthreads(); // probabilities written; the last reader of KV is done
+			for (int x = tid; x < SWA_KB * dvp; x += nth) {
+				const int jj = x / dvp, c = x % dvp;
+				KV[jj * ldkv + c] = (jj < nbk && c < dv) ? ldf(vc + (size_t) ((j0 + jj) % a.ring) * (G * dv) + g * dv + c) : 0.f;
+			}
+			__syncthreads();
+			const int NTv = dvp >> 2;
+			for (int tile = tid; tile < (Rg >> 2) * NTv; tile += nth) {
+				const int mt = tile / NTv, nt = tile % NTv, rb = g * Rg + 4 * mt;
+				float acc[4][4] = {};
+#pragma unroll 8
+				for (int jj = 0; jj < SWA_KB; jj++) {
+					const float4 pv = *reinterpret_cast<const float4*>(Pr + (size_t) jj * R + rb);
+					const float4 vv = *reinterpret_cast<const float4*>(KV + jj * ldkv + 4 * nt);
+					const float pa[4] = {pv.x, pv.y, pv.z, pv.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+					for (int i = 0; i < 4; i++)
+#pragma unroll
+						for (int u = 0; u < 4; u++) acc[i][u] = fmaf(pa[i], va[u], acc[i][u]);
+				}
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					float4* op = reinterpret_cast<float4*>(O + (size_t) (rb + i) * dvp + 4 * nt);
+					const float al = alpha[rb + i];
+					float4 o = *op;
+					o.x = fmaf(al, o.x, acc[i][0]); o.y = fmaf(al, o.y, acc[i][1]); o.z = fmaf(al, o.z, acc[i][2]); o.w = fmaf(al, o.w, acc[i][3]);
+					*op = o;
+				}
+			}
+		}
+	}
+	__syncthreads();
+	for (int x = tid; x < nq * H * dv; x += nth) {
+		const int c = x % dv, h = (x / dv) % H, q = x / (dv * H), row = (h / rep) * Rg + (h % rep) * TQ + q;
+		const int t = t0 + q;
+		const float acc = O[(size_t) row * dvp + c];
+		if (a.n_splits == 1) {
+			float o = acc / lrun[row];
+			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + h * dv + c]);
+			a.out[(size_t) t * (H * dv) + h * dv + c] = o;
+		} else a.part_o[((size_t) t * a.n_splits + sp) * (H * dv) + h * dv + c] = acc;
+	}
+	if (a.n_splits > 1)
+		for (int x = tid; x < nq * H; x += nth) {
+			const int h = x % H, q = x / H, row = (h / rep) * Rg + (h % rep) * TQ + q;
+			float* pml = a.part_ml + ((size_t) (t0 + q) * a.n_splits + sp) * (H * 2);
+			pml[2 * h] = mrun[row];
+			pml[2 * h + 1] = lrun[row];
+		}
+}
+
 // ---- gated linear recurrence (HGRN2) --------------------------------------------------------------------------------------------
 struct Hgrn2Args {
 	const float* proj; // (T, ld): per head h, q at q_off + h * d, forget pre-activation at f_off + h * d, v at v_off + h * dv
@@ -470,6 +695,7 @@ struct Hgrn2Args {
 	float* state;        // (H, d, dv) fp32, carried between steps
 	const SeqStep* step;
 	float* out;          // (T, H * dv)
+	int max_rows;        // most tokens a step can bring (the launch sizes its shared memory by it)
 };
 constexpr int HG_TC = 8; // tokens staged at a time
 
@@ -529,6 +755,136 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 	for (int x = tid; x < d * dv; x += nth) st[x] = S[x];
 }
 inline size_t hgrn2_smem_bytes(int d, int dv) { return sizeof(float) * ((size_t) d * dv + 2 * (size_t) HG_TC * d + (size_t) HG_TC * dv); }
+
+// ---- the same recurrence, the state's columns spread over warps, CTAs and a thread-block cluster ---------------------------------
+// Column c of a head's state evolves on its own: S[:, c] <- f .* S[:, c] + (1 - f) v[c], o[c] = q . S[:, c].  A warp owns HG_CW columns
+// with the d channels across its lanes (DPL per lane) in registers; a CTA owns warps x HG_CW columns; the CTAs of one head form a
+// cluster (grid.x = cluster size <= 8).  Tokens are staged HG_TT at a time (activations applied once per CTA); the lanes' partial dot
+// products of a tile (HG_TT x HG_CW = 32 values) are summed with one transposed butterfly (31 shuffles instead of 160).  The RMS norm
+// over a head's dv columns needs every CTA's share: each keeps its per-token sums of squares in shared memory, and after one cluster
+// barrier reads the others' through distributed shared memory and scales the rows it wrote.
+constexpr int HG_CW = 4, HG_TT = 8;
+
+// v[k] of every lane -> lane k gets the sum over lanes of v[k]
+__device__ __forceinline__ float warp_sum_transposed32(float (&v)[32], int lane) {
+#pragma unroll
+	for (int s = 16; s >= 1; s >>= 1) {
+		const bool up = (lane & s) != 0;
+#pragma unroll
+		for (int k = 0; k < s; k++) {
+			const float send = up ? v[k] : v[k + s];
+			const float keep = up ? v[k + s] : v[k];
+			v[k] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+		}
+	}
+	return v[0];
+}
+
+template <int DPL>
+__global__ void hgrn2_cols_kernel(Hgrn2Args a) {
+	namespace cg = cooperative_groups;
+	cg::cluster_group cluster = cg::this_cluster();
+	extern __shared__ float sm[];
+	constexpr int DP = DPL * 32;
+	const int d = a.d, dv = a.dv, h = blockIdx.y, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
+	const int cpb = nw * HG_CW, c_blk = blockIdx.x * cpb, c0 = c_blk + warp * HG_CW;
+	float* fch = sm;                   // HG_TT * DP   forget gate (0 beyond d)
+	float* gch = fch + HG_TT * DP;     // HG_TT * DP   1 - f
+	float* qch = gch + HG_TT * DP;     // HG_TT * DP   silu(q)
+	float* vch = qch + HG_TT * DP;     // HG_TT * cpb
+	float* och = vch + HG_TT * cpb;    // HG_TT * cpb  o before the norm
+	float* ssq = och + HG_TT * cpb;    // max_rows     this CTA's share of sum_c o[t][c]^2
+	float* st = a.state + (size_t) h * d * dv;
+	const int T = min(a.step->n, a.max_rows);
+	float S[HG_CW][DPL];
+#pragma unroll
+	for (int cc = 0; cc < HG_CW; cc++)
+#pragma unroll
+		for (int k = 0; k < DPL; k++) {
+			const int i = lane + 32 * k, c = c0 + cc;
+			S[cc][k] = (i < d && c < dv) ? st[(size_t) i * dv + c] : 0.f;
+		}
+	for (int t0 = 0; t0 < T; t0 += HG_TT) {
+		const int nt = min(HG_TT, T - t0);
+		__syncthreads();
+		for (int x = tid; x < nt * DP; x += nth) {
+			const int tt = x / DP, i = x % DP;
+			float f = 0.f, g = 0.f, q = 0.f;
+			if (i < d) {
+				const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
+				const float z = row[a.f_off + h * d + i] + (a.f_bias ? a.f_bias[h * d + i] : 0.f);
+				const float lo = a.lower ? a.lower[h * d + i] : 0.f;
+				f = lo + (1.f - lo) * sigmoidf_(z);
+				g = 1.f - f;
+				const float zq = row[a.q_off + h * d + i];
+				q = zq * sigmoidf_(zq);
+			}
+			fch[x] = f; gch[x] = g; qch[x] = q;
+		}
+		for (int x = tid; x < nt * cpb; x += nth) {
+			const int tt = x / cpb, c = c_blk + x % cpb;
+			vch[x] = c < dv ? a.proj[(size_t) (t0 + tt) * a.ld + a.v_off + h * dv + c] : 0.f;
+		}
+		__syncthreads();
+		float p[HG_TT * HG_CW];
+#pragma unroll
+		for (int tt = 0; tt < HG_TT; tt++) {
+#pragma unroll
+			for (int cc = 0; cc < HG_CW; cc++) p[tt * HG_CW + cc] = 0.f;
+			if (tt < nt) {
+				float v[HG_CW];
+#pragma unroll
+				for (int cc = 0; cc < HG_CW; cc++) v[cc] = vch[tt * cpb + warp * HG_CW + cc];
+#pragma unroll
+				for (int k = 0; k < DPL; k++) {
+					const float fi = fch[tt * DP + lane + 32 * k], gi = gch[tt * DP + lane + 32 * k], qi = qch[tt * DP + lane + 32 * k];
+#pragma unroll
+					for (int cc = 0; cc < HG_CW; cc++) {
+						S[cc][k] = fmaf(fi, S[cc][k], gi * v[cc]);
+						p[tt * HG_CW + cc] = fmaf(S[cc][k], qi, p[tt * HG_CW + cc]);
+					}
+				}
+			}
+		}
+		const float o = warp_sum_transposed32(p, lane); // lane = tt * HG_CW + cc
+		och[(lane / HG_CW) * cpb + warp * HG_CW + lane % HG_CW] = o;
+		__syncthreads();
+		for (int tt = warp; tt < nt; tt += nw) {
+			float ss = 0.f;
+			float* orow = a.out + (size_t) (t0 + tt) * (a.H * dv) + h * dv;
+			for (int cc = lane; cc < cpb; cc += 32)
+				if (c_blk + cc < dv) {
+					const float x = och[tt * cpb + cc];
+					orow[c_blk + cc] = x;
+					ss = fmaf(x, x, ss);
+				}
+			ss = warp_sum(ss);
+			if (lane == 0) ssq[t0 + tt] = ss;
+		}
+	}
+#pragma unroll
+	for (int cc = 0; cc < HG_CW; cc++)
+#pragma unroll
+		for (int k = 0; k < DPL; k++) {
+			const int i = lane + 32 * k, c = c0 + cc;
+			if (i < d && c < dv) st[(size_t) i * dv + c] = S[cc][k];
+		}
+	if (!a.norm_w) return; // uniform over the cluster: nobody waits
+	cluster.sync();
+	const unsigned nb = cluster.num_blocks();
+	for (int t = warp; t < T; t += nw) {
+		float tot = lane < (int) nb ? cluster.map_shared_rank(ssq, lane)[t] : 0.f;
+		tot = warp_sum(tot);
+		const float r = 1.f / sqrtf(tot / (float) dv + a.eps);
+		float* orow = a.out + (size_t) t * (a.H * dv) + h * dv;
+		for (int cc = lane; cc < cpb; cc += 32)
+			if (c_blk + cc < dv) orow[c_blk + cc] = orow[c_blk + cc] * r * a.norm_w[c_blk + cc];
+	}
+	cluster.sync(); // no CTA leaves while another still reads its sums
+}
+inline size_t hgrn2_cols_smem_bytes(int dpl, int warps, int max_rows) {
+	return sizeof(float) * (3 * (size_t) HG_TT * dpl * 32 + 2 * (size_t) HG_TT * warps * HG_CW + (size_t) max_rows);
+}
 
 // ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
 static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
@@ -619,12 +975,46 @@ static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, c
 	return launch_check("hc_norm");
 }
 
-// rows: tokens of the step; cache_f32: element type of the ring.  With n_splits > 1 the merge kernel follows.
-static inline int launch_swa(const SwaArgs& a, int rows, bool cache_f32, cudaStream_t s) {
-	const size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
-	XALM_TRY(swa_prepare(a.H, a.d, a.dv));
-	if (cache_f32) swa_attn_kernel<float><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
-	else swa_attn_kernel<__nv_bfloat16><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
+// Queries per CTA of the tiled kernel: the most (<= 16, <= rows rounded up to a power of two) whose tile leaves room for two CTAs
+// per SM, else for one; 0 if not even one query fits (then the one-query kernel above runs).
+static inline int swa_pick_tq(int H, int G, int d, int dv, int rows) {
+	int cap = 1;
+	while (cap < rows && cap < 16) cap *= 2;
+	if (rows <= 4) cap = 1; // short steps: a CTA per token, keys split over CTAs
+	for (const size_t budget : {(size_t) 110 * 1024, (size_t) 220 * 1024})
+		for (int tq = cap; tq >= 1; tq >>= 1)
+			if (swa_tile_smem_floats(H, G, d, dv, tq) * 4 <= budget) return tq;
+	return 0;
+}
+
+// rows: tokens of the step; cache_f32: element type of the ring.  With n_splits > 1 the merge kernel follows.  Returns the number of
+// launches through *launches (1 or 2) when it is given.
+static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s, int* launches = nullptr) {
+	const int tq = swa_pick_tq(a.H, a.G, a.d, a.dv, rows);
+	if (a.n_splits <= 0) { // enough CTAs for two waves, at least two key blocks each
+		const int qblocks = tq ? (rows + tq - 1) / tq : rows;
+		const long long keys = std::min<long long>((long long) a.ring, (long long) (a.window < 0x7fffffff ? a.window : a.ring) + (tq ? tq : 1));
+		int want = std::max(1, 296 / std::max(1, qblocks));
+		want = (int) std::min<long long>(want, std::max<long long>(1, keys / (2 * SWA_KB)));
+		a.n_splits = (a.part_o && a.part_ml) ? std::max(1, std::min(want, a.part_cap / std::max(1, rows))) : 1;
+	}
+	if (launches) *launches = a.n_splits > 1 ? 2 : 1;
+	if (tq) {
+		a.tq = tq;
+		const size_t smem = swa_tile_smem_floats(a.H, a.G, a.d, a.dv, tq) * 4;
+		if (smem > 48 * 1024) {
+			if (cache_f32) XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_tile_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+			else XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_tile_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+		}
+		const dim3 grid((rows + tq - 1) / tq, a.n_splits);
+		if (cache_f32) swa_tile_kernel<float><<<grid, 256, smem, s>>>(a);
+		else swa_tile_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(a);
+	} else {
+		const size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
+		XALM_TRY(swa_prepare(a.H, a.d, a.dv));
+		if (cache_f32) swa_attn_kernel<float><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
+		else swa_attn_kernel<__nv_bfloat16><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
+	}
 	XALM_TRY(launch_check("swa_attn"));
 	if (a.n_splits > 1) {
 		swa_merge_kernel<<<rows, 256, 0, s>>>(a);
@@ -633,7 +1023,48 @@ static inline int launch_swa(const SwaArgs& a, int rows, bool cache_f32, cudaStr
 	return XALM_OK;
 }
 
+// max_rows: an upper bound of the step's tokens known on the host.  The cluster kernel takes d <= 256 and dv <= 1024; anything else
+// (and max_rows beyond its shared memory) runs the one-CTA-per-head kernel.
+template <int DPL>
+static inline int launch_hgrn2_cols(const Hgrn2Args& a, int warps, int nb, cudaStream_t s) {
+	const size_t smem = hgrn2_cols_smem_bytes(DPL, warps, a.max_rows);
+	if (smem > 48 * 1024) XALM_CUDA_CHECK(cudaFuncSetAttribute(hgrn2_cols_kernel<DPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem));
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3(nb, a.H);
+	cfg.blockDim = dim3(warps * 32);
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = s;
+	cudaLaunchAttribute at[1];
+	at[0].id = cudaLaunchAttributeClusterDimension;
+	at[0].val.clusterDim.x = nb; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+	cfg.attrs = at;
+	cfg.numAttrs = 1;
+	const cudaError_t e = cudaLaunchKernelEx(&cfg, hgrn2_cols_kernel<DPL>, a);
+	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "hgrn2 launch failed: %s", cudaGetErrorString(e));
+	return XALM_OK;
+}
+
+// warps per CTA of the cluster kernel for dv columns: the fewest of 4 .. 32 that keep a head within 8 CTAs
+static inline int hgrn2_cols_warps(int dv) {
+	int warps = 4;
+	while (warps < 32 && (dv + warps * HG_CW - 1) / (warps * HG_CW) > 8) warps *= 2;
+	return warps;
+}
+static inline bool hgrn2_cols_ok(int d, int dv, int max_rows) {
+	const int warps = hgrn2_cols_warps(dv), nb = (dv + warps * HG_CW - 1) / (warps * HG_CW), dpl = (d + 31) / 32;
+	return nb <= 8 && dpl <= 8 && max_rows > 0 && hgrn2_cols_smem_bytes(dpl <= 1 ? 1 : dpl <= 2 ? 2 : dpl <= 4 ? 4 : 8, warps, max_rows) <= 160 * 1024;
+}
+
 static inline int launch_hgrn2(const Hgrn2Args& a, cudaStream_t s) {
+	const int warps = hgrn2_cols_warps(a.dv);
+	const int nb = (a.dv + warps * HG_CW - 1) / (warps * HG_CW);
+	const int dpl = (a.d + 31) / 32;
+	if (hgrn2_cols_ok(a.d, a.dv, a.max_rows)) {
+		if (dpl <= 1) return launch_hgrn2_cols<1>(a, warps, nb, s);
+		if (dpl <= 2) return launch_hgrn2_cols<2>(a, warps, nb, s);
+		if (dpl <= 4) return launch_hgrn2_cols<4>(a, warps, nb, s);
+		return launch_hgrn2_cols<8>(a, warps, nb, s);
+	}
 	const size_t smem = hgrn2_smem_bytes(a.d, a.dv);
 	XALM_TRY(hgrn2_prepare(a.d, a.dv));
 	hgrn2_kernel<<<a.H, std::min(1024, (a.dv + 31) / 32 * 32), smem, s>>>(a);

@@ -116,7 +116,7 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	int chunk = 256;
 	float *xs = nullptr, *h = nullptr, *proj = nullptr, *att = nullptr, *ro = nullptr, *ol = nullptr, *orr = nullptr, *y = nullptr, *logits = nullptr;
 	float *part_o = nullptr, *part_ml = nullptr, *layer_sums = nullptr;
-	int max_splits = 1, keep_layers = 0;
+	int part_cap = 0, keep_layers = 0; // part_cap: (token, key split) pairs the attention's partial buffers hold
 	int* d_tokens = nullptr;
 	SeqStep* d_step = nullptr;
 	float* h_logits = nullptr; // pinned, chunk x vocab
@@ -378,15 +378,16 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		sa.scale = L.L.scale; sa.softcap = L.L.softcap;
 		sa.r1 = L.r1; sa.r2 = L.r2; sa.talk = L.talk;
 		sa.step = m->d_step; sa.out = m->att;
-		sa.n_splits = n <= 4 ? m->max_splits : 1;
-		sa.part_o = m->part_o; sa.part_ml = m->part_ml;
-		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s));
-		*nl += sa.n_splits > 1 ? 2 : 1;
+		sa.n_splits = 0; // the launcher spreads the keys over CTAs when the step has few tokens
+		sa.part_o = m->part_o; sa.part_ml = m->part_ml; sa.part_cap = m->part_cap;
+		int swa_launches = 1;
+		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s, &swa_launches));
+		*nl += swa_launches;
 		Hgrn2Args ha = {};
 		ha.proj = m->proj; ha.ld = (int) m->proj_ld; ha.q_off = L.off_rq; ha.f_off = L.off_rf; ha.v_off = L.off_rv;
 		ha.H = Hr; ha.d = dr; ha.dv = dvr;
 		ha.f_bias = L.fb; ha.lower = L.lower; ha.norm_w = L.rnorm; ha.eps = m->eps;
-		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro;
+		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro; ha.max_rows = m->chunk;
 		XALM_TRY(launch_hgrn2(ha, s));
 		(*nl)++;
 		RowsEpi est;
@@ -462,7 +463,7 @@ int run_pass(Nb* m, const int* tokens, int n, int want) {
 		int cnt = 0;
 		if (!m->last_launches) { // count once, without running: the same sequence the graph holds
 			cnt = 1 + (want ? 2 : 0);
-			for (const Layer& L : m->layers) cnt += 7 + (m->max_splits > 1 ? 1 : 0) + (L.has_mlp ? 3 : 0) + (m->keep_layers ? 1 : 0);
+			for (const Layer& L : m->layers) cnt += 7 + 1 + (L.has_mlp ? 3 : 0) + (m->keep_layers ? 1 : 0);
 			nl = cnt;
 		}
 	} else {
@@ -598,7 +599,7 @@ int nb_finalize(Nb* m) {
 	XALM_TRY(upload_rows(m, {T("embed")}, W, false, &m->embed, nullptr));
 	XALM_TRY(upload_rows(m, {T("head")}, W, false, &m->w_head, &m->m_head));
 	XALM_TRY(upload_vec(m, "final.norm", &m->final_norm));
-	size_t max_proj = 0, max_att = 0, max_ro = 0, max_ff = 1, max_hdv = 0;
+	size_t max_proj = 0, max_att = 0, max_ro = 0, max_ff = 1, max_hdv = 0, max_h = 1;
 	int max_ring = 1;
 	for (size_t li = 0; li < m->layers.size(); li++) {
 		Layer& L = m->layers[li];
@@ -654,9 +655,12 @@ int nb_finalize(Nb* m) {
 		max_ro = std::max(max_ro, (size_t) Hr * dvr);
 		if (L.has_mlp) max_ff = std::max(max_ff, (size_t) L.ff);
 		max_hdv = std::max(max_hdv, (size_t) H * dv);
+		max_h = std::max(max_h, (size_t) H);
 		const size_t asm_ = swa_smem_bytes(H, d, dv), hsm = hgrn2_smem_bytes(dr, dvr);
-		if (asm_ > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: attention heads need %zu bytes of shared memory", li, asm_);
-		if (hsm > 200 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: recurrence state needs %zu bytes of shared memory", li, hsm);
+		if (!swa_pick_tq(H, G, d, dv, m->chunk) && asm_ > 200 * 1024)
+			return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: attention heads need %zu bytes of shared memory", li, asm_);
+		if (!hgrn2_cols_ok(dr, dvr, m->chunk) && hsm > 200 * 1024)
+			return set_error(XALM_ERR_UNSUPPORTED, "layer %zu: recurrence state needs %zu bytes of shared memory", li, hsm);
 		XALM_TRY(swa_prepare(H, d, dv));
 		XALM_TRY(hgrn2_prepare(dr, dvr));
 	}
@@ -693,7 +697,7 @@ int nb_finalize(Nb* m) {
 	}
 	m->proj_ld = (max_proj + 3) / 4 * 4;
 	const size_t C = (size_t) m->chunk;
-	m->max_splits = std::max(1, std::min(32, (max_ring + 4 * SWA_KB - 1) / (4 * SWA_KB)));
+	m->part_cap = std::max(4 * 64, 4 * m->chunk); // one-token steps: up to 64 key splits; passes of a prompt: up to 4 per token
 	XALM_TRY(dev_alloc(m, &m->xs, (size_t) S * C * W));
 	XALM_TRY(dev_alloc(m, &m->h, C * W));
 	XALM_TRY(dev_alloc(m, &m->proj, C * m->proj_ld));
@@ -703,8 +707,8 @@ int nb_finalize(Nb* m) {
 	XALM_TRY(dev_alloc(m, &m->orr, C * W));
 	XALM_TRY(dev_alloc(m, &m->y, C * max_ff));
 	XALM_TRY(dev_alloc(m, &m->logits, C * m->vocab));
-	XALM_TRY(dev_alloc(m, &m->part_o, (size_t) 4 * m->max_splits * max_hdv));
-	XALM_TRY(dev_alloc(m, &m->part_ml, (size_t) 4 * m->max_splits * max_hdv)); // >= 4 x splits x H x 2
+	XALM_TRY(dev_alloc(m, &m->part_o, (size_t) m->part_cap * max_hdv));
+	XALM_TRY(dev_alloc(m, &m->part_ml, (size_t) m->part_cap * 2 * max_h));
 	if (m->keep_layers) XALM_TRY(dev_alloc(m, &m->layer_sums, m->layers.size() * C * W, true));
 	XALM_TRY(dev_alloc(m, &m->d_tokens, C));
 	XALM_TRY(dev_alloc(m, &m->d_step, 1));
