@@ -129,6 +129,11 @@ struct RowsEpi {
 	void* kc = nullptr;
 	void* vc = nullptr;
 	const SeqStep* step = nullptr;
+	// SPLIT_KV, plain columns: [silu_off, silu_off + silu_n) -> z * sigmoid(z); [gate_off, gate_off + gate_n) -> a lower-bounded sigmoid gate
+	// lo + (1 - lo) * sigmoid(z + bias) with lo = gate_lower[col - gate_off] (NULL: 0) and bias = gate_bias[col - gate_off] (NULL: 0)
+	int silu_off = 0, silu_n = 0, gate_off = 0, gate_n = 0;
+	const float* gate_bias = nullptr;
+	const float* gate_lower = nullptr;
 	// GLU: even column = gate, odd = up: y = min(g, limit) * sigmoid(alpha * .) * (clamp(u, +-limit) + 1)
 	float limit = 0.f, alpha = 1.702f;
 	// HC: xs[t'][row][col] = sum_s hmix[s * S + t'] xs[s][row][col] + hout[t'] * scale[col] * value   (hmix / hout NULL: identity / ones)
@@ -166,7 +171,16 @@ __device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, in
 	switch (e.kind) {
 		case EPI_STORE: e.out[(size_t) row * e.ldo + col] = v; break;
 		case EPI_SPLIT_KV: {
-			if (col < e.n_plain) { e.out[(size_t) row * e.ldo + col] = v; break; }
+			if (col < e.n_plain) {
+				if (col >= e.silu_off && col < e.silu_off + e.silu_n) v = v * sigmoidf_(v);
+				else if (col >= e.gate_off && col < e.gate_off + e.gate_n) {
+					const int c = col - e.gate_off;
+					const float lo = e.gate_lower ? e.gate_lower[c] : 0.f;
+					v = lo + (1.f - lo) * sigmoidf_(v + (e.gate_bias ? e.gate_bias[c] : 0.f));
+				}
+				e.out[(size_t) row * e.ldo + col] = v;
+				break;
+			}
 			const int slot = (e.step->pos0 + row) % e.ring;
 			const int ck = col - e.n_plain;
 			if (ck < e.kdim) {
@@ -248,54 +262,68 @@ static __global__ void rows_epilogue_kernel(const float* __restrict__ src, int l
 	}
 }
 
-// ---- the same for T <= TB tokens: a warp per pair of output columns -------------------------------------------------------------
-template <typename WT, int TB>
+// ---- the same for T <= TB tokens: a warp per pair of output columns, or KS warps of the CTA per pair (each a slice of K, summed through
+// shared memory) when there are too few columns to fill the machine ---------------------------------------------------------------
+template <typename WT, int TB, int KS>
 __global__ void __launch_bounds__(256) rows_matvec_kernel(const float* __restrict__ A, int lda, const WT* __restrict__ W, int T, int N, int K, RowsEpi e) {
-	const int lane = threadIdx.x & 31;
-	const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+	__shared__ float red[8][TB][2];
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ks = warp % KS;
+	const int pair = blockIdx.x * (8 / KS) + warp / KS;
 	const int c0 = pair * 2;
-	if (c0 >= N) return;
-	const bool two = c0 + 1 < N;
-	const WT* w0 = W + (size_t) c0 * K;
-	const WT* w1 = W + (size_t) (two ? c0 + 1 : c0) * K;
+	const bool live = c0 < N, two = c0 + 1 < N;
 	float acc0[TB] = {}, acc1[TB] = {};
-	const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
-	if (vec) {
-		for (int k = lane * 8; k < K; k += 256) {
-			float a0[8], a1[8];
-			ld8(w0 + k, a0);
-			ld8(w1 + k, a1);
+	if (live) {
+		const WT* w0 = W + (size_t) c0 * K;
+		const WT* w1 = W + (size_t) (two ? c0 + 1 : c0) * K;
+		const bool vec = (K % 8 == 0) && (lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+		if (vec) {
+#pragma unroll 2
+			for (int k = (ks * 32 + lane) * 8; k < K; k += 256 * KS) {
+				float a0[8], a1[8];
+				ld8(w0 + k, a0);
+				ld8(w1 + k, a1);
 #pragma unroll
-			for (int t = 0; t < TB; t++) {
-				if (t < T) {
-					float x[8];
-					ld8(A + (size_t) t * lda + k, x);
+				for (int t = 0; t < TB; t++) {
+					if (t < T) {
+						float x[8];
+						ld8(A + (size_t) t * lda + k, x);
 #pragma unroll
-					for (int i = 0; i < 8; i++) {
-						acc0[t] = fmaf(a0[i], x[i], acc0[t]);
-						acc1[t] = fmaf(a1[i], x[i], acc1[t]);
+						for (int i = 0; i < 8; i++) {
+							acc0[t] = fmaf(a0[i], x[i], acc0[t]);
+							acc1[t] = fmaf(a1[i], x[i], acc1[t]);
+						}
 					}
 				}
 			}
+		} else {
+			for (int k = ks * 32 + lane; k < K; k += 32 * KS) {
+				const float a0 = ldf(w0 + k), a1 = ldf(w1 + k);
+#pragma unroll
+				for (int t = 0; t < TB; t++)
+					if (t < T) {
+						const float x = A[(size_t) t * lda + k];
+						acc0[t] = fmaf(a0, x, acc0[t]);
+						acc1[t] = fmaf(a1, x, acc1[t]);
+					}
+			}
 		}
-	} else {
-		for (int k = lane; k < K; k += 32) {
-			const float a0 = ldf(w0 + k), a1 = ldf(w1 + k);
+#pragma unroll
+		for (int t = 0; t < TB; t++) {
+			acc0[t] = warp_sum(acc0[t]);
+			acc1[t] = warp_sum(acc1[t]);
+		}
+	}
+	if (KS > 1) {
+		if (lane == 0)
+#pragma unroll
+			for (int t = 0; t < TB; t++) { red[warp][t][0] = acc0[t]; red[warp][t][1] = acc1[t]; }
+		__syncthreads();
+		if (ks == 0 && lane == 0)
 #pragma unroll
 			for (int t = 0; t < TB; t++)
-				if (t < T) {
-					const float x = A[(size_t) t * lda + k];
-					acc0[t] = fmaf(a0, x, acc0[t]);
-					acc1[t] = fmaf(a1, x, acc1[t]);
-				}
-		}
+				for (int j = 1; j < KS; j++) { acc0[t] += red[warp + j][t][0]; acc1[t] += red[warp + j][t][1]; }
 	}
-#pragma unroll
-	for (int t = 0; t < TB; t++) {
-		acc0[t] = warp_sum(acc0[t]);
-		acc1[t] = warp_sum(acc1[t]);
-	}
-	if (lane == 0) {
+	if (live && ks == 0 && lane == 0) {
 #pragma unroll
 		for (int t = 0; t < TB; t++) {
 			if (t >= T) break;
@@ -329,6 +357,8 @@ struct SwaArgs {
 	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes.  0: the launcher chooses (part_cap bounds it)
 	int part_cap;      // (row, split) pairs part_o / part_ml have room for (only read when n_splits == 0)
 	int tq;            // queries per CTA of the tiled kernel (set by the launcher)
+	unsigned* tickets; // one zeroed counter per query tile, or NULL.  With it the tiled kernel's last-arriving key split joins the parts itself
+	                   // (and resets the counter); without it swa_merge_kernel follows
 	float* part_o;     // (T, n_splits, H * dv)
 	float* part_ml;    // (T, n_splits, H, 2)
 };
@@ -439,27 +469,28 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 
 inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
 
-// joins the key splits of one-token steps: out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
-static __global__ void swa_merge_kernel(SwaArgs a) {
-	const int t = blockIdx.x, H = a.H, dv = a.dv;
-	for (int x = threadIdx.x; x < H * dv; x += blockDim.x) {
-		const int h = x / dv;
+// joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
+__device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
+	const int H = a.H, dv = a.dv;
+	for (int x = tid; x < rows * H * dv; x += nth) {
+		const int t = t_first + x / (H * dv), hc = x % (H * dv), h = hc / dv;
+		const float* pml0 = a.part_ml + (size_t) t * a.n_splits * (H * 2) + 2 * h;
 		float m = -INFINITY;
-		for (int s = 0; s < a.n_splits; s++) m = fmaxf(m, a.part_ml[((size_t) t * a.n_splits + s) * (H * 2) + 2 * h]);
+		for (int s = 0; s < a.n_splits; s++) m = fmaxf(m, __ldcg(pml0 + (size_t) s * (H * 2)));
 		float num = 0.f, den = 0.f;
 		for (int s = 0; s < a.n_splits; s++) {
-			const float* pml = a.part_ml + ((size_t) t * a.n_splits + s) * (H * 2);
-			const float ms = pml[2 * h];
+			const float ms = __ldcg(pml0 + (size_t) s * (H * 2));
 			if (ms == -INFINITY) continue;
 			const float w = expf(ms - m);
-			num = fmaf(w, a.part_o[((size_t) t * a.n_splits + s) * (H * dv) + x], num);
-			den = fmaf(w, pml[2 * h + 1], den);
+			num = fmaf(w, __ldcg(a.part_o + ((size_t) t * a.n_splits + s) * (H * dv) + hc), num);
+			den = fmaf(w, __ldcg(pml0 + (size_t) s * (H * 2) + 1), den);
 		}
 		float o = num / den;
-		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
-		a.out[(size_t) t * (H * dv) + x] = o;
+		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
+		a.out[(size_t) t * (H * dv) + hc] = o;
 	}
 }
+static __global__ void swa_merge_kernel(SwaArgs a) { swa_merge_rows(a, blockIdx.x, 1, threadIdx.x, blockDim.x); }
 
 // ---- the same attention, tiled: a CTA takes `tq` consecutive queries with ALL their heads (the score mixing needs every head's score
 // of a query-key pair) and walks the keys SWA_KB at a time ------------------------------------------------------------------------
@@ -490,6 +521,40 @@ __host__ __device__ inline size_t swa_tile_smem_floats(int H, int G, int d, int 
 	const SwaTile t = swa_tile_dims(H, G, d, dv, tq);
 	const size_t kv = (size_t) SWA_KB * (t.ldq > t.dvp ? t.ldq : t.dvp);
 	return (size_t) t.R * t.ldq + kv + 2 * (size_t) SWA_KB * t.R + (size_t) t.R * t.dvp + (size_t) H * t.Hp + 3 * (size_t) t.R;
+}
+
+// rows j0 .. j0 + SWA_KB of one kv group's slice of the ring (w elements at column col0 of rows of row_elems) -> dst[jj * ldd + c] in fp32,
+// zero beyond nbk rows and beyond w columns (up to wp).  16-byte loads, two in flight per thread, when the slice allows.
+template <typename CT>
+__device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* base, int row_elems, int col0, int w, int wp, int j0, int nbk, int ring,
+                                              int tid, int nth) {
+	if (((w | row_elems | col0) & 7) == 0) {
+		const int cpr = w >> 3, total = SWA_KB * cpr;
+		for (int x0 = tid; x0 < total; x0 += 2 * nth) {
+			float v[2][8];
+#pragma unroll
+			for (int u = 0; u < 2; u++) {
+				const int x = x0 + u * nth, jj = x / cpr, c = (x % cpr) << 3;
+				if (x < total && jj < nbk) ld8(base + (size_t) ((j0 + jj) % ring) * row_elems + col0 + c, v[u]);
+				else
+#pragma unroll
+					for (int i = 0; i < 8; i++) v[u][i] = 0.f;
+			}
+#pragma unroll
+			for (int u = 0; u < 2; u++) {
+				const int x = x0 + u * nth, jj = x / cpr, c = (x % cpr) << 3;
+				if (x < total) {
+					*reinterpret_cast<float4*>(dst + jj * ldd + c) = make_float4(v[u][0], v[u][1], v[u][2], v[u][3]);
+					*reinterpret_cast<float4*>(dst + jj * ldd + c + 4) = make_float4(v[u][4], v[u][5], v[u][6], v[u][7]);
+				}
+			}
+		}
+	} else {
+		for (int x = tid; x < SWA_KB * wp; x += nth) {
+			const int jj = x / wp, k = x % wp;
+			dst[jj * ldd + k] = (jj < nbk && k < w) ? ldf(base + (size_t) ((j0 + jj) % ring) * row_elems + col0 + k) : 0.f;
+		}
+	}
 }
 
 template <typename CT>
@@ -548,10 +613,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- raw scores, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
-			for (int x = tid; x < SWA_KB * dp; x += nth) {
-				const int jj = x / dp, k = x % dp;
-				KV[jj * ldkv + k] = (jj < nbk && k < d) ? ldf(kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + g * d + k) : 0.f;
-			}
+			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, a.ring, tid, nth);
 			__syncthreads();
 			for (int tile = tid; tile < (Rg >> 2) * 8; tile += nth) {
 				const int mt = tile >> 3, nt = tile & 7;
@@ -633,10 +695,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- O <- alpha O + P^T V, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // probabilities written; the last reader of KV is done
-			for (int x = tid; x < SWA_KB * dvp; x += nth) {
-				const int jj = x / dvp, c = x % dvp;
-				KV[jj * ldkv + c] = (jj < nbk && c < dv) ? ldf(vc + (size_t) ((j0 + jj) % a.ring) * (G * dv) + g * dv + c) : 0.f;
-			}
+			swa_load_tile(KV, ldkv, vc, G * dv, g * dv, dv, dvp, j0, nbk, a.ring, tid, nth);
 			__syncthreads();
 			const int NTv = dvp >> 2;
 			for (int tile = tid; tile < (Rg >> 2) * NTv; tile += nth) {
@@ -681,6 +740,21 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			pml[2 * h] = mrun[row];
 			pml[2 * h + 1] = lrun[row];
 		}
+	if (a.n_splits > 1 && a.tickets) { // the split that arrives last joins the parts of this query tile
+		__shared__ int last;
+		__threadfence();
+		__syncthreads();
+		if (tid == 0) {
+			const unsigned got = atomicAdd(a.tickets + blockIdx.x, 1u);
+			last = got == (unsigned) a.n_splits - 1u;
+			if (last) a.tickets[blockIdx.x] = 0u;
+		}
+		__syncthreads();
+		if (last) {
+			__threadfence();
+			swa_merge_rows(a, t0, nq, tid, nth);
+		}
+	}
 }
 
 // ---- gated linear recurrence (HGRN2) --------------------------------------------------------------------------------------------
@@ -696,6 +770,7 @@ struct Hgrn2Args {
 	const SeqStep* step;
 	float* out;          // (T, H * dv)
 	int max_rows;        // most tokens a step can bring (the launch sizes its shared memory by it)
+	int activated;       // 1: proj already holds the forget gate and silu(q) (the producing product's epilogue applied them)
 };
 constexpr int HG_TC = 8; // tokens staged at a time
 
@@ -715,11 +790,11 @@ static __global__ void hgrn2_kernel(Hgrn2Args a) {
 		for (int x = tid; x < nt * d; x += nth) {
 			const int tt = x / d, i = x % d;
 			const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
-			const float z = row[a.f_off + h * d + i] + (a.f_bias ? a.f_bias[h * d + i] : 0.f);
+			const float z = row[a.f_off + h * d + i] + (a.f_bias && !a.activated ? a.f_bias[h * d + i] : 0.f);
 			const float lo = a.lower ? a.lower[h * d + i] : 0.f;
-			fch[x] = lo + (1.f - lo) * sigmoidf_(z);
+			fch[x] = a.activated ? z : lo + (1.f - lo) * sigmoidf_(z);
 			const float zq = row[a.q_off + h * d + i];
-			qch[x] = zq * sigmoidf_(zq);
+			qch[x] = a.activated ? zq : zq * sigmoidf_(zq);
 		}
 		__syncthreads();
 		for (int c = tid; c < dv; c += nth) {
@@ -786,13 +861,11 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 	cg::cluster_group cluster = cg::this_cluster();
 	extern __shared__ float sm[];
 	constexpr int DP = DPL * 32;
+	constexpr int NPF = HG_TT * DP / 128; // (channel, token) pairs a thread of the smallest CTA stages per tile
 	const int d = a.d, dv = a.dv, h = blockIdx.y, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
 	const int cpb = nw * HG_CW, c_blk = blockIdx.x * cpb, c0 = c_blk + warp * HG_CW;
-	float* fch = sm;                   // HG_TT * DP   forget gate (0 beyond d)
-	float* gch = fch + HG_TT * DP;     // HG_TT * DP   1 - f
-	float* qch = gch + HG_TT * DP;     // HG_TT * DP   silu(q)
-	float* vch = qch + HG_TT * DP;     // HG_TT * cpb
-	float* och = vch + HG_TT * cpb;    // HG_TT * cpb  o before the norm
+	const int tile_floats = 3 * HG_TT * DP + HG_TT * cpb; // f | 1 - f | silu(q) | v of one tile
+	float* och = sm + 2 * tile_floats; // HG_TT * cpb  o before the norm
 	float* ssq = och + HG_TT * cpb;    // max_rows     this CTA's share of sum_c o[t][c]^2
 	float* st = a.state + (size_t) h * d * dv;
 	const int T = min(a.step->n, a.max_rows);
@@ -804,28 +877,59 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			const int i = lane + 32 * k, c = c0 + cc;
 			S[cc][k] = (i < d && c < dv) ? st[(size_t) i * dv + c] : 0.f;
 		}
-	for (int t0 = 0; t0 < T; t0 += HG_TT) {
+	// The next tile's inputs travel through registers while this tile is scanned: raw loads are issued before the scan, the
+	// activations (unless the producer already applied them) and the stores to the other buffer come after it.
+	float rf[NPF], rq[NPF], rv = 0.f;
+	auto fetch = [&](int t0) {
 		const int nt = min(HG_TT, T - t0);
-		__syncthreads();
-		for (int x = tid; x < nt * DP; x += nth) {
-			const int tt = x / DP, i = x % DP;
-			float f = 0.f, g = 0.f, q = 0.f;
-			if (i < d) {
+#pragma unroll
+		for (int u = 0; u < NPF; u++) {
+			const int x = tid + u * nth, tt = x / DP, i = x % DP;
+			rf[u] = 0.f; rq[u] = 0.f;
+			if (x < HG_TT * DP && tt < nt && i < d) {
 				const float* row = a.proj + (size_t) (t0 + tt) * a.ld;
-				const float z = row[a.f_off + h * d + i] + (a.f_bias ? a.f_bias[h * d + i] : 0.f);
-				const float lo = a.lower ? a.lower[h * d + i] : 0.f;
-				f = lo + (1.f - lo) * sigmoidf_(z);
-				g = 1.f - f;
-				const float zq = row[a.q_off + h * d + i];
-				q = zq * sigmoidf_(zq);
+				rf[u] = row[a.f_off + h * d + i];
+				rq[u] = row[a.q_off + h * d + i];
 			}
-			fch[x] = f; gch[x] = g; qch[x] = q;
 		}
-		for (int x = tid; x < nt * cpb; x += nth) {
-			const int tt = x / cpb, c = c_blk + x % cpb;
-			vch[x] = c < dv ? a.proj[(size_t) (t0 + tt) * a.ld + a.v_off + h * dv + c] : 0.f;
+		const int tt = tid / cpb, c = c_blk + tid % cpb; // nth == HG_TT * cpb
+		rv = (tt < nt && c < dv) ? a.proj[(size_t) (t0 + tt) * a.ld + a.v_off + h * dv + c] : 0.f;
+	};
+	auto stage = [&](float* buf, int t0) {
+		const int nt = min(HG_TT, T - t0);
+#pragma unroll
+		for (int u = 0; u < NPF; u++) {
+			const int x = tid + u * nth, tt = x / DP, i = x % DP;
+			if (x < HG_TT * DP) {
+				float f = 0.f, g = 0.f, q = 0.f;
+				if (tt < nt && i < d) {
+					if (a.activated) { f = rf[u]; q = rq[u]; }
+					else {
+						const float lo = a.lower ? a.lower[h * d + i] : 0.f;
+						f = lo + (1.f - lo) * sigmoidf_(rf[u] + (a.f_bias ? a.f_bias[h * d + i] : 0.f));
+						q = rq[u] * sigmoidf_(rq[u]);
+					}
+					g = 1.f - f;
+				}
+				buf[x] = f; buf[HG_TT * DP + x] = g; buf[2 * HG_TT * DP + x] = q;
+			}
 		}
-		__syncthreads();
+		buf[3 * HG_TT * DP + tid] = rv;
+	};
+	if (T > 0) {
+		fetch(0);
+		stage(sm, 0);
+	}
+	__syncthreads();
+	int cur = 0;
+	for (int t0 = 0; t0 < T; t0 += HG_TT, cur ^= 1) {
+		const int nt = min(HG_TT, T - t0);
+		const float* fch = sm + cur * tile_floats;
+		const float* gch = fch + HG_TT * DP;
+		const float* qch = gch + HG_TT * DP;
+		const float* vch = qch + HG_TT * DP;
+		const bool more = t0 + HG_TT < T;
+		if (more) fetch(t0 + HG_TT);
 		float p[HG_TT * HG_CW];
 #pragma unroll
 		for (int tt = 0; tt < HG_TT; tt++) {
@@ -848,6 +952,7 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 		}
 		const float o = warp_sum_transposed32(p, lane); // lane = tt * HG_CW + cc
 		och[(lane / HG_CW) * cpb + warp * HG_CW + lane % HG_CW] = o;
+		if (more) stage(sm + (cur ^ 1) * tile_floats, t0 + HG_TT);
 		__syncthreads();
 		for (int tt = warp; tt < nt; tt += nw) {
 			float ss = 0.f;
@@ -861,6 +966,7 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 			ss = warp_sum(ss);
 			if (lane == 0) ssq[t0 + tt] = ss;
 		}
+		__syncthreads(); // och is free for the next tile
 	}
 #pragma unroll
 	for (int cc = 0; cc < HG_CW; cc++)
@@ -883,7 +989,7 @@ __global__ void hgrn2_cols_kernel(Hgrn2Args a) {
 	cluster.sync(); // no CTA leaves while another still reads its sums
 }
 inline size_t hgrn2_cols_smem_bytes(int dpl, int warps, int max_rows) {
-	return sizeof(float) * (3 * (size_t) HG_TT * dpl * 32 + 2 * (size_t) HG_TT * warps * HG_CW + (size_t) max_rows);
+	return sizeof(float) * (2 * (3 * (size_t) HG_TT * dpl * 32 + (size_t) HG_TT * warps * HG_CW) + (size_t) HG_TT * warps * HG_CW + (size_t) max_rows);
 }
 
 // ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
@@ -917,14 +1023,25 @@ static inline int norm_threads(int width) { return width >= 1024 ? 256 : width >
 // out(T,N) = A(T,K) . W(N,K)^T with epilogue e, IEEE fp32 arithmetic; W is bf16 or fp32
 static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf16, int T, int N, int K, const RowsEpi& e, cudaStream_t s) {
 	if (T <= 4) {
-		const int pairs = (N + 1) / 2, grid = (pairs + 7) / 8;
+		const int pairs = (N + 1) / 2;
+		int ks = 1; // warps per column pair: enough CTAs for two per SM, each slice of K at least 256 long
+		while (ks < 8 && (pairs * ks + 7) / 8 < 296 && K >= 512 * ks) ks *= 2;
+		const int grid = (pairs * ks + 7) / 8;
+#define XALM_ROWS_MATVEC(WT_, TB_)                                                                                                   \
+	do {                                                                                                                             \
+		if (ks == 1) rows_matvec_kernel<WT_, TB_, 1><<<grid, 256, 0, s>>>(A, lda, (const WT_*) W, T, N, K, e);                       \
+		else if (ks == 2) rows_matvec_kernel<WT_, TB_, 2><<<grid, 256, 0, s>>>(A, lda, (const WT_*) W, T, N, K, e);                  \
+		else if (ks == 4) rows_matvec_kernel<WT_, TB_, 4><<<grid, 256, 0, s>>>(A, lda, (const WT_*) W, T, N, K, e);                  \
+		else rows_matvec_kernel<WT_, TB_, 8><<<grid, 256, 0, s>>>(A, lda, (const WT_*) W, T, N, K, e);                               \
+	} while (0)
 		if (w_bf16) {
-			if (T == 1) rows_matvec_kernel<__nv_bfloat16, 1><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
-			else rows_matvec_kernel<__nv_bfloat16, 4><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
+			if (T == 1) XALM_ROWS_MATVEC(__nv_bfloat16, 1);
+			else XALM_ROWS_MATVEC(__nv_bfloat16, 4);
 		} else {
-			if (T == 1) rows_matvec_kernel<float, 1><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
-			else rows_matvec_kernel<float, 4><<<grid, 256, 0, s>>>(A, lda, (const float*) W, T, N, K, e);
+			if (T == 1) XALM_ROWS_MATVEC(float, 1);
+			else XALM_ROWS_MATVEC(float, 4);
 		}
+#undef XALM_ROWS_MATVEC
 	} else {
 		const dim3 grid((N + 63) / 64, (T + 63) / 64);
 		if (w_bf16) rows_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(A, lda, (const __nv_bfloat16*) W, T, N, K, e);
@@ -998,7 +1115,8 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		want = (int) std::min<long long>(want, std::max<long long>(1, keys / (2 * SWA_KB)));
 		a.n_splits = (a.part_o && a.part_ml) ? std::max(1, std::min(want, a.part_cap / std::max(1, rows))) : 1;
 	}
-	if (launches) *launches = a.n_splits > 1 ? 2 : 1;
+	if (!tq) a.tickets = nullptr;
+	if (launches) *launches = a.n_splits > 1 && !a.tickets ? 2 : 1;
 	if (tq) {
 		a.tq = tq;
 		const size_t smem = swa_tile_smem_floats(a.H, a.G, a.d, a.dv, tq) * 4;
@@ -1016,7 +1134,7 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		else swa_attn_kernel<__nv_bfloat16><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
 	}
 	XALM_TRY(launch_check("swa_attn"));
-	if (a.n_splits > 1) {
+	if (a.n_splits > 1 && !a.tickets) {
 		swa_merge_kernel<<<rows, 256, 0, s>>>(a);
 		XALM_TRY(launch_check("swa_merge"));
 	}
@@ -1052,7 +1170,8 @@ static inline int hgrn2_cols_warps(int dv) {
 }
 static inline bool hgrn2_cols_ok(int d, int dv, int max_rows) {
 	const int warps = hgrn2_cols_warps(dv), nb = (dv + warps * HG_CW - 1) / (warps * HG_CW), dpl = (d + 31) / 32;
-	return nb <= 8 && dpl <= 8 && max_rows > 0 && hgrn2_cols_smem_bytes(dpl <= 1 ? 1 : dpl <= 2 ? 2 : dpl <= 4 ? 4 : 8, warps, max_rows) <= 160 * 1024;
+	const int regs = dpl <= 1 ? 64 : dpl <= 4 ? 96 : 216; // per thread, as compiled; a CTA's registers must fit one SM's file
+	return nb <= 8 && dpl <= 8 && warps * 32 * regs <= 65536 && max_rows > 0 && hgrn2_cols_smem_bytes(dpl <= 1 ? 1 : dpl <= 2 ? 2 : dpl <= 4 ? 4 : 8, warps, max_rows) <= 160 * 1024;
 }
 
 static inline int launch_hgrn2(const Hgrn2Args& a, cudaStream_t s) {

@@ -116,6 +116,7 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	int chunk = 256;
 	float *xs = nullptr, *h = nullptr, *proj = nullptr, *att = nullptr, *ro = nullptr, *ol = nullptr, *orr = nullptr, *y = nullptr, *logits = nullptr;
 	float *part_o = nullptr, *part_ml = nullptr, *layer_sums = nullptr;
+	unsigned* tickets = nullptr; // per query tile: arrivals of the attention's key splits
 	int part_cap = 0, keep_layers = 0; // part_cap: (token, key split) pairs the attention's partial buffers hold
 	int* d_tokens = nullptr;
 	SeqStep* d_step = nullptr;
@@ -368,6 +369,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		ein.n_plain = L.n_plain; ein.kdim = G * d; ein.vdim = G * dv; ein.ring = L.ring;
 		ein.cache_f32 = m->precision == XALM_PRECISION_F32;
 		ein.kc = L.kc; ein.vc = L.vc; ein.step = m->d_step;
+		ein.silu_off = L.off_rq; ein.silu_n = Hr * dr; ein.gate_off = L.off_rf; ein.gate_n = Hr * dr; ein.gate_bias = L.fb; ein.gate_lower = L.lower;
 		XALM_TRY(rows_product(m, m->h, W, L.w_in, &L.t_in, n, L.n_in, W, ein, nl));
 		SwaArgs sa = {};
 		sa.q = m->proj; sa.gate = L.has_gate ? m->proj : nullptr;
@@ -379,7 +381,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		sa.r1 = L.r1; sa.r2 = L.r2; sa.talk = L.talk;
 		sa.step = m->d_step; sa.out = m->att;
 		sa.n_splits = 0; // the launcher spreads the keys over CTAs when the step has few tokens
-		sa.part_o = m->part_o; sa.part_ml = m->part_ml; sa.part_cap = m->part_cap;
+		sa.part_o = m->part_o; sa.part_ml = m->part_ml; sa.part_cap = m->part_cap; sa.tickets = m->tickets;
 		int swa_launches = 1;
 		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s, &swa_launches));
 		*nl += swa_launches;
@@ -387,7 +389,7 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		ha.proj = m->proj; ha.ld = (int) m->proj_ld; ha.q_off = L.off_rq; ha.f_off = L.off_rf; ha.v_off = L.off_rv;
 		ha.H = Hr; ha.d = dr; ha.dv = dvr;
 		ha.f_bias = L.fb; ha.lower = L.lower; ha.norm_w = L.rnorm; ha.eps = m->eps;
-		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro; ha.max_rows = m->chunk;
+		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro; ha.max_rows = m->chunk; ha.activated = 1;
 		XALM_TRY(launch_hgrn2(ha, s));
 		(*nl)++;
 		RowsEpi est;
@@ -463,7 +465,7 @@ int run_pass(Nb* m, const int* tokens, int n, int want) {
 		int cnt = 0;
 		if (!m->last_launches) { // count once, without running: the same sequence the graph holds
 			cnt = 1 + (want ? 2 : 0);
-			for (const Layer& L : m->layers) cnt += 7 + 1 + (L.has_mlp ? 3 : 0) + (m->keep_layers ? 1 : 0);
+			for (const Layer& L : m->layers) cnt += 7 + (L.has_mlp ? 3 : 0) + (m->keep_layers ? 1 : 0);
 			nl = cnt;
 		}
 	} else {
@@ -709,6 +711,7 @@ int nb_finalize(Nb* m) {
 	XALM_TRY(dev_alloc(m, &m->logits, C * m->vocab));
 	XALM_TRY(dev_alloc(m, &m->part_o, (size_t) m->part_cap * max_hdv));
 	XALM_TRY(dev_alloc(m, &m->part_ml, (size_t) m->part_cap * 2 * max_h));
+	XALM_TRY(dev_alloc(m, &m->tickets, C, true));
 	if (m->keep_layers) XALM_TRY(dev_alloc(m, &m->layer_sums, m->layers.size() * C * W, true));
 	XALM_TRY(dev_alloc(m, &m->d_tokens, C));
 	XALM_TRY(dev_alloc(m, &m->d_step, 1));
