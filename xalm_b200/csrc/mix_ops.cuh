@@ -365,110 +365,6 @@ struct SwaArgs {
 
 constexpr int SWA_KB = 32; // keys per block
 
-template <typename CT>
-__global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
-	extern __shared__ float sm[];
-	const int H = a.H, G = a.G, d = a.d, dv = a.dv, rep = H / G;
-	float* qs = sm;                  // H * d
-	float* sc = qs + H * d;          // H * KB raw scores
-	float* pr = sc + H * SWA_KB;     // H * KB mixed scores, then probabilities
-	float* tk = pr + H * SWA_KB;     // H * H
-	float* mrun = tk + H * H;        // H
-	float* lrun = mrun + H;          // H
-	float* alpha = lrun + H;         // H
-	float* O = alpha + H;            // H * dv
-	const CT* kc = reinterpret_cast<const CT*>(a.kc);
-	const CT* vc = reinterpret_cast<const CT*>(a.vc);
-	const int t = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, nth = blockDim.x;
-	const int i = a.step->pos0 + t;
-	const int j_first = max(0, i - a.window + 1);
-	const int nk = i - j_first + 1;
-	int per = (nk + a.n_splits - 1) / a.n_splits;
-	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
-	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
-
-	for (int x = tid; x < H * d; x += nth) qs[x] = a.q[(size_t) t * a.ldq + a.q_off + x];
-	for (int x = tid; x < H * H; x += nth) tk[x] = a.talk ? a.talk[x] : (x / H == x % H ? 1.f : 0.f);
-	for (int x = tid; x < H; x += nth) { mrun[x] = -INFINITY; lrun[x] = 0.f; }
-	for (int x = tid; x < H * dv; x += nth) O[x] = 0.f;
-	__syncthreads();
-
-	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
-		const int nb = min(SWA_KB, je - j0);
-		// raw scores: scale, soft cap, distance bias
-		for (int x = tid; x < H * SWA_KB; x += nth) {
-			const int h = x / SWA_KB, jj = x % SWA_KB;
-			float s = 0.f;
-			if (jj < nb) {
-				const int j = j0 + jj;
-				const CT* kr = kc + (size_t) (j % a.ring) * (G * d) + (h / rep) * d;
-				const float* qh = qs + h * d;
-				float acc = 0.f;
-				for (int c = 0; c < d; c++) acc = fmaf(qh[c], ldf(kr + c), acc);
-				s = acc * a.scale;
-				if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-				if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) (i - j));
-			}
-			sc[x] = s;
-		}
-		__syncthreads();
-		// mix the heads' scores
-		for (int x = tid; x < H * SWA_KB; x += nth) {
-			const int h = x / SWA_KB, jj = x % SWA_KB;
-			float s = -INFINITY;
-			if (jj < nb) {
-				if (a.talk) {
-					s = 0.f;
-					for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * SWA_KB + jj], s);
-				} else s = sc[x];
-			}
-			pr[x] = s;
-		}
-		__syncthreads();
-		// online softmax, a warp per head
-		for (int h = tid >> 5; h < H; h += nth >> 5) {
-			const int lane = tid & 31;
-			const float s = pr[h * SWA_KB + lane]; // SWA_KB == 32
-			const float bm = warp_max(s);
-			const float m_old = mrun[h], m_new = fmaxf(m_old, bm);
-			const float p = (lane < nb) ? expf(s - m_new) : 0.f;
-			const float ps = warp_sum(p);
-			pr[h * SWA_KB + lane] = p;
-			if (lane == 0) {
-				const float al = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
-				alpha[h] = al;
-				mrun[h] = m_new;
-				lrun[h] = lrun[h] * al + ps;
-			}
-		}
-		__syncthreads();
-		// O <- alpha O + P V
-		for (int x = tid; x < H * dv; x += nth) {
-			const int h = x / dv, c = x % dv;
-			float acc = O[x] * alpha[h];
-			const CT* vcol = vc + (h / rep) * dv + c;
-			const float* ph = pr + h * SWA_KB;
-			for (int jj = 0; jj < nb; jj++) acc = fmaf(ph[jj], ldf(vcol + (size_t) ((j0 + jj) % a.ring) * (G * dv)), acc);
-			O[x] = acc;
-		}
-		__syncthreads();
-	}
-	if (a.n_splits == 1) {
-		for (int x = tid; x < H * dv; x += nth) {
-			float o = O[x] / lrun[x / dv];
-			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
-			a.out[(size_t) t * (H * dv) + x] = o;
-		}
-	} else {
-		float* po = a.part_o + ((size_t) t * a.n_splits + sp) * (H * dv);
-		float* pml = a.part_ml + ((size_t) t * a.n_splits + sp) * (H * 2);
-		for (int x = tid; x < H * dv; x += nth) po[x] = O[x];
-		for (int x = tid; x < H; x += nth) { pml[2 * x] = mrun[x]; pml[2 * x + 1] = lrun[x]; }
-	}
-}
-
-inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
-
 // joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
 __device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
 	const int H = a.H, dv = a.dv;
@@ -491,6 +387,172 @@ __device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, in
 	}
 }
 static __global__ void swa_merge_kernel(SwaArgs a) { swa_merge_rows(a, blockIdx.x, 1, threadIdx.x, blockDim.x); }
+// With key splits and a ticket counter per query tile: the split that arrives last joins the parts of the tile's rows and leaves the
+// counter at zero for the next launch.  Every thread of the CTA calls it after writing its parts.
+__device__ __forceinline__ void swa_join_last(const SwaArgs& a, int tile, int t_first, int rows, int tid, int nth) {
+	__shared__ int last;
+	__threadfence();
+	__syncthreads();
+	if (tid == 0) {
+		const unsigned got = atomicAdd(a.tickets + tile, 1u);
+		last = got == (unsigned) a.n_splits - 1u;
+		if (last) a.tickets[tile] = 0u;
+	}
+	__syncthreads();
+	if (last) {
+		__threadfence();
+		swa_merge_rows(a, t_first, rows, tid, nth);
+	}
+}
+
+
+template <typename CT>
+__global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
+	extern __shared__ float sm[];
+	const int H = a.H, G = a.G, d = a.d, dv = a.dv, rep = H / G;
+	float* qs = sm;                  // H * d
+	float* sc = qs + H * d;          // H * KB raw scores
+	float* pr = sc + H * SWA_KB;     // H * KB mixed scores, then probabilities
+	float* tk = pr + H * SWA_KB;     // H * H
+	float* mrun = tk + H * H;        // H
+	float* lrun = mrun + H;          // H
+	float* alpha = lrun + H;         // H
+	float* O = alpha + H;            // H * dv
+	const CT* kc = reinterpret_cast<const CT*>(a.kc);
+	const CT* vc = reinterpret_cast<const CT*>(a.vc);
+	const int t = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
+	const bool vec8 = ((d | (G * d)) & 7) == 0;
+	if (t >= a.step->n) return;
+	const int i = a.step->pos0 + t;
+	const int j_first = max(0, i - a.window + 1);
+	const int nk = i - j_first + 1;
+	int per = (nk + a.n_splits - 1) / a.n_splits;
+	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
+	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
+
+	for (int x = tid; x < H * d; x += nth) qs[x] = a.q[(size_t) t * a.ldq + a.q_off + x];
+	for (int x = tid; x < H * H; x += nth) tk[x] = a.talk ? a.talk[x] : (x / H == x % H ? 1.f : 0.f);
+	for (int x = tid; x < H; x += nth) { mrun[x] = -INFINITY; lrun[x] = 0.f; }
+	for (int x = tid; x < H * dv; x += nth) O[x] = 0.f;
+	__syncthreads();
+
+	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
+		const int nb = min(SWA_KB, je - j0);
+		// raw scores: a warp per key, its lanes along the channels (16-byte loads), up to four heads of the key's group per read of
+		// the key; then scale, soft cap, distance bias
+		for (int jj = warp; jj < SWA_KB; jj += nw) {
+			if (jj >= nb) {
+				for (int h = lane; h < H; h += 32) sc[h * SWA_KB + jj] = 0.f;
+				continue;
+			}
+			const int j = j0 + jj;
+			const CT* krow = kc + (size_t) (j % a.ring) * (G * d);
+			for (int g = 0; g < G; g++)
+				for (int hr = 0; hr < rep; hr += 4) {
+					const CT* kr = krow + g * d;
+					const float* qh = qs + (size_t) (g * rep + hr) * d;
+					const int nh = min(4, rep - hr);
+					float acc[4] = {0.f, 0.f, 0.f, 0.f};
+					if (vec8) {
+						for (int c = lane * 8; c < d; c += 256) {
+							float kk[8];
+							ld8(kr + c, kk);
+#pragma unroll
+							for (int u = 0; u < 4; u++)
+								if (u < nh) {
+									const float4 q0 = *reinterpret_cast<const float4*>(qh + u * d + c), q1 = *reinterpret_cast<const float4*>(qh + u * d + c + 4);
+									acc[u] = fmaf(q0.x, kk[0], acc[u]); acc[u] = fmaf(q0.y, kk[1], acc[u]); acc[u] = fmaf(q0.z, kk[2], acc[u]); acc[u] = fmaf(q0.w, kk[3], acc[u]);
+									acc[u] = fmaf(q1.x, kk[4], acc[u]); acc[u] = fmaf(q1.y, kk[5], acc[u]); acc[u] = fmaf(q1.z, kk[6], acc[u]); acc[u] = fmaf(q1.w, kk[7], acc[u]);
+								}
+						}
+					} else {
+						for (int c = lane; c < d; c += 32) {
+							const float kk = ldf(kr + c);
+#pragma unroll
+							for (int u = 0; u < 4; u++)
+								if (u < nh) acc[u] = fmaf(qh[u * d + c], kk, acc[u]);
+						}
+					}
+#pragma unroll
+					for (int u = 0; u < 4; u++) acc[u] = warp_sum(acc[u]);
+					if (lane < nh) {
+						const int h = g * rep + hr + lane;
+						float s = (lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3]) * a.scale;
+						if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+						if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) (i - j));
+						sc[h * SWA_KB + jj] = s;
+					}
+				}
+		}
+		__syncthreads();
+		// mix the heads' scores
+		for (int x = tid; x < H * SWA_KB; x += nth) {
+			const int h = x / SWA_KB, jj = x % SWA_KB;
+			float s = -INFINITY;
+			if (jj < nb) {
+				if (a.talk) {
+					s = 0.f;
+					for (int g = 0; g < H; g++) s = fmaf(tk[h * H + g], sc[g * SWA_KB + jj], s);
+				} else s = sc[x];
+			}
+			pr[x] = s;
+		}
+		__syncthreads();
+		// online softmax, a warp per head
+		for (int h = warp; h < H; h += nw) {
+			const float s = pr[h * SWA_KB + lane]; // SWA_KB == 32
+			const float bm = warp_max(s);
+			const float m_old = mrun[h], m_new = fmaxf(m_old, bm);
+			const float p = (lane < nb) ? expf(s - m_new) : 0.f;
+			const float ps = warp_sum(p);
+			pr[h * SWA_KB + lane] = p;
+			if (lane == 0) {
+				const float al = (m_old == -INFINITY) ? 0.f : expf(m_old - m_new);
+				alpha[h] = al;
+				mrun[h] = m_new;
+				lrun[h] = lrun[h] * al + ps;
+			}
+		}
+		__syncthreads();
+		// O <- alpha O + P V: a thread per value column of a kv group, up to four heads of the group per read of V
+		for (int x = tid; x < G * dv; x += nth) {
+			const int g = x / dv, c = x % dv;
+			const CT* vcol = vc + g * dv + c;
+			for (int hr = 0; hr < rep; hr += 4) {
+				const int h0 = g * rep + hr, nh = min(4, rep - hr);
+				float acc[4];
+#pragma unroll
+				for (int u = 0; u < 4; u++) acc[u] = u < nh ? O[(size_t) (h0 + u) * dv + c] * alpha[h0 + u] : 0.f;
+				for (int jj = 0; jj < nb; jj++) {
+					const float v = ldf(vcol + (size_t) ((j0 + jj) % a.ring) * (G * dv));
+#pragma unroll
+					for (int u = 0; u < 4; u++)
+						if (u < nh) acc[u] = fmaf(pr[(h0 + u) * SWA_KB + jj], v, acc[u]);
+				}
+#pragma unroll
+				for (int u = 0; u < 4; u++)
+					if (u < nh) O[(size_t) (h0 + u) * dv + c] = acc[u];
+			}
+		}
+		__syncthreads();
+	}
+	if (a.n_splits == 1) {
+		for (int x = tid; x < H * dv; x += nth) {
+			float o = O[x] / lrun[x / dv];
+			if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + x]);
+			a.out[(size_t) t * (H * dv) + x] = o;
+		}
+	} else {
+		float* po = a.part_o + ((size_t) t * a.n_splits + sp) * (H * dv);
+		float* pml = a.part_ml + ((size_t) t * a.n_splits + sp) * (H * 2);
+		for (int x = tid; x < H * dv; x += nth) po[x] = O[x];
+		for (int x = tid; x < H; x += nth) { pml[2 * x] = mrun[x]; pml[2 * x + 1] = lrun[x]; }
+		if (a.tickets) swa_join_last(a, blockIdx.x, t, 1, tid, nth);
+	}
+}
+
+inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
+
 
 // ---- the same attention, tiled: a CTA takes `tq` consecutive queries with ALL their heads (the score mixing needs every head's score
 // of a query-key pair) and walks the keys SWA_KB at a time ------------------------------------------------------------------------
@@ -740,21 +802,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			pml[2 * h] = mrun[row];
 			pml[2 * h + 1] = lrun[row];
 		}
-	if (a.n_splits > 1 && a.tickets) { // the split that arrives last joins the parts of this query tile
-		__shared__ int last;
-		__threadfence();
-		__syncthreads();
-		if (tid == 0) {
-			const unsigned got = atomicAdd(a.tickets + blockIdx.x, 1u);
-			last = got == (unsigned) a.n_splits - 1u;
-			if (last) a.tickets[blockIdx.x] = 0u;
-		}
-		__syncthreads();
-		if (last) {
-			__threadfence();
-			swa_merge_rows(a, t0, nq, tid, nth);
-		}
-	}
+	if (a.n_splits > 1 && a.tickets) swa_join_last(a, blockIdx.x, t0, nq, tid, nth);
 }
 
 // ---- gated linear recurrence (HGRN2) --------------------------------------------------------------------------------------------
@@ -1095,9 +1143,9 @@ static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, c
 // Queries per CTA of the tiled kernel: the most (<= 16, <= rows rounded up to a power of two) whose tile leaves room for two CTAs
 // per SM, else for one; 0 if not even one query fits (then the one-query kernel above runs).
 static inline int swa_pick_tq(int H, int G, int d, int dv, int rows) {
+	if (rows <= 4 && swa_smem_bytes(H, d, dv) <= 200 * 1024) return 0; // short steps: the one-query kernel, a CTA per (token, key split)
 	int cap = 1;
 	while (cap < rows && cap < 16) cap *= 2;
-	if (rows <= 4) cap = 1; // short steps: a CTA per token, keys split over CTAs
 	for (const size_t budget : {(size_t) 110 * 1024, (size_t) 220 * 1024})
 		for (int tq = cap; tq >= 1; tq >>= 1)
 			if (swa_tile_smem_floats(H, G, d, dv, tq) * 4 <= budget) return tq;
@@ -1112,10 +1160,9 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		const int qblocks = tq ? (rows + tq - 1) / tq : rows;
 		const long long keys = std::min<long long>((long long) a.ring, (long long) (a.window < 0x7fffffff ? a.window : a.ring) + (tq ? tq : 1));
 		int want = std::max(1, 296 / std::max(1, qblocks));
-		want = (int) std::min<long long>(want, std::max<long long>(1, keys / (2 * SWA_KB)));
+		want = (int) std::min<long long>(want, std::max<long long>(1, tq ? keys / (2 * SWA_KB) : (keys + SWA_KB - 1) / SWA_KB)); // key blocks per CTA: >= 2 (tiled), 1 (one query)
 		a.n_splits = (a.part_o && a.part_ml) ? std::max(1, std::min(want, a.part_cap / std::max(1, rows))) : 1;
 	}
-	if (!tq) a.tickets = nullptr;
 	if (launches) *launches = a.n_splits > 1 && !a.tickets ? 2 : 1;
 	if (tq) {
 		a.tq = tq;
