@@ -451,6 +451,7 @@ def run_family_workload(args):
             llama_cfg = X.parse_config(synth.metadata_strings(llama_full), ctx)
             for fam in ("nabalix", "llama"):
                 if fam == "nabalix":
+                    capi.tune("seq_chunk", args.seq_chunk)  # positions per pass of a prompt (the Llama arm takes the prompt in one pass)
                     m = build_nabalix(z, args.seed, ctx, stream.cuda_stream)
                 else:
                     m, _ = build_model_streaming(llama_full, llama_cfg, T.BF16, args.seed, False, stream=stream.cuda_stream)
@@ -490,7 +491,7 @@ def run_family_workload(args):
                       "steps": args.steps, "warmup": args.warmup, "ms_per_step": rows[first]["nabalix"]["decode_ms"], "higher_is_better": True,
                       "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": "families", "prompt_tokens": n_tok, "sizes": {s: FAMILY_SIZES[s] for s in rows},
-                                 "l2": "a 192 MB buffer is written between timed iterations", "peak_gbs": measured_peak_gbs()[0]},
+                                 "seq_chunk": args.seq_chunk, "l2": "a 192 MB buffer is written between timed iterations", "peak_gbs": measured_peak_gbs()[0]},
                       "families": rows, "clocks": clocks.summary()}))
 
 
@@ -515,6 +516,7 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families"],
                     help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input; "
                          "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes")
+    ap.add_argument("--seq-chunk", type=int, default=1024, help="families workload: positions per pass of a Nabalix prompt")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="families workload: which of " + ",".join(FAMILY_SIZES))
     ap.add_argument("--tokens", type=int, default=4096, help="perplexity workload: tokens per step")
     ap.add_argument("--split", type=int, default=0, help="perplexity workload: operand precision (0 = library default 3; 1 = plain fp16)")

@@ -367,19 +367,36 @@ constexpr int SWA_KB = 32; // keys per block
 
 // joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
 __device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
-	const int H = a.H, dv = a.dv;
+	const int H = a.H, dv = a.dv, ns = a.n_splits;
 	for (int x = tid; x < rows * H * dv; x += nth) {
 		const int t = t_first + x / (H * dv), hc = x % (H * dv), h = hc / dv;
-		const float* pml0 = a.part_ml + (size_t) t * a.n_splits * (H * 2) + 2 * h;
+		const float* pml0 = a.part_ml + (size_t) t * ns * (H * 2) + 2 * h;
+		const float* po0 = a.part_o + (size_t) t * ns * (H * dv) + hc;
 		float m = -INFINITY;
-		for (int s = 0; s < a.n_splits; s++) m = fmaxf(m, __ldcg(pml0 + (size_t) s * (H * 2)));
+		for (int s0 = 0; s0 < ns; s0 += 8) { // eight loads in flight
+			float ms[8];
+#pragma unroll
+			for (int u = 0; u < 8; u++) ms[u] = s0 + u < ns ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2)) : -INFINITY;
+#pragma unroll
+			for (int u = 0; u < 8; u++) m = fmaxf(m, ms[u]);
+		}
 		float num = 0.f, den = 0.f;
-		for (int s = 0; s < a.n_splits; s++) {
-			const float ms = __ldcg(pml0 + (size_t) s * (H * 2));
-			if (ms == -INFINITY) continue;
-			const float w = expf(ms - m);
-			num = fmaf(w, __ldcg(a.part_o + ((size_t) t * a.n_splits + s) * (H * dv) + hc), num);
-			den = fmaf(w, __ldcg(pml0 + (size_t) s * (H * 2) + 1), den);
+		for (int s0 = 0; s0 < ns; s0 += 8) {
+			float ms[8], ls[8], os[8];
+#pragma unroll
+			for (int u = 0; u < 8; u++) {
+				const bool in = s0 + u < ns;
+				ms[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2)) : -INFINITY;
+				ls[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2) + 1) : 0.f;
+				os[u] = in ? __ldcg(po0 + (size_t) (s0 + u) * (H * dv)) : 0.f;
+			}
+#pragma unroll
+			for (int u = 0; u < 8; u++)
+				if (ms[u] != -INFINITY) {
+					const float w = expf(ms[u] - m);
+					num = fmaf(w, os[u], num);
+					den = fmaf(w, ls[u], den);
+				}
 		}
 		float o = num / den;
 		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
@@ -438,52 +455,63 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 
 	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
 		const int nb = min(SWA_KB, je - j0);
-		// raw scores: a warp per key, its lanes along the channels (16-byte loads), up to four heads of the key's group per read of
-		// the key; then scale, soft cap, distance bias
-		for (int jj = warp; jj < SWA_KB; jj += nw) {
-			if (jj >= nb) {
-				for (int h = lane; h < H; h += 32) sc[h * SWA_KB + jj] = 0.f;
-				continue;
-			}
-			const int j = j0 + jj;
-			const CT* krow = kc + (size_t) (j % a.ring) * (G * d);
-			for (int g = 0; g < G; g++)
-				for (int hr = 0; hr < rep; hr += 4) {
-					const CT* kr = krow + g * d;
-					const float* qh = qs + (size_t) (g * rep + hr) * d;
-					const int nh = min(4, rep - hr);
-					float acc[4] = {0.f, 0.f, 0.f, 0.f};
-					if (vec8) {
-						for (int c = lane * 8; c < d; c += 256) {
-							float kk[8];
-							ld8(kr + c, kk);
+		// raw scores: a warp takes keys warp, warp + 8, ... of the block (four with 256 threads), its lanes along the channels, eight
+		// each; the loads of all four keys are issued before the first product, and up to four heads of the group share them.
+		// Then scale, soft cap, distance bias.
+		for (int g = 0; g < G; g++)
+			for (int hr = 0; hr < rep; hr += 4) {
+				const float* qh = qs + (size_t) (g * rep + hr) * d;
+				const int nh = min(4, rep - hr);
+				float acc[4][4] = {}; // [key][head]
+				for (int c = lane * 8; c < d; c += 256) {
+					float kk[4][8];
 #pragma unroll
-							for (int u = 0; u < 4; u++)
-								if (u < nh) {
-									const float4 q0 = *reinterpret_cast<const float4*>(qh + u * d + c), q1 = *reinterpret_cast<const float4*>(qh + u * d + c + 4);
-									acc[u] = fmaf(q0.x, kk[0], acc[u]); acc[u] = fmaf(q0.y, kk[1], acc[u]); acc[u] = fmaf(q0.z, kk[2], acc[u]); acc[u] = fmaf(q0.w, kk[3], acc[u]);
-									acc[u] = fmaf(q1.x, kk[4], acc[u]); acc[u] = fmaf(q1.y, kk[5], acc[u]); acc[u] = fmaf(q1.z, kk[6], acc[u]); acc[u] = fmaf(q1.w, kk[7], acc[u]);
-								}
-						}
-					} else {
-						for (int c = lane; c < d; c += 32) {
-							const float kk = ldf(kr + c);
+					for (int kq = 0; kq < 4; kq++) {
+						const int jj = warp + kq * 8;
+						const CT* kr = kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + g * d + c;
+						if (jj < nb && vec8) ld8(kr, kk[kq]);
+						else
 #pragma unroll
-							for (int u = 0; u < 4; u++)
-								if (u < nh) acc[u] = fmaf(qh[u * d + c], kk, acc[u]);
-						}
+							for (int e8 = 0; e8 < 8; e8++) kk[kq][e8] = (jj < nb && c + e8 < d) ? ldf(kr + e8) : 0.f;
 					}
 #pragma unroll
-					for (int u = 0; u < 4; u++) acc[u] = warp_sum(acc[u]);
-					if (lane < nh) {
-						const int h = g * rep + hr + lane;
-						float s = (lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3]) * a.scale;
-						if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-						if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) (i - j));
-						sc[h * SWA_KB + jj] = s;
+					for (int u = 0; u < 4; u++)
+						if (u < nh) {
+							float qv[8];
+							if (vec8) {
+								const float4 q0 = *reinterpret_cast<const float4*>(qh + u * d + c), q1 = *reinterpret_cast<const float4*>(qh + u * d + c + 4);
+								qv[0] = q0.x; qv[1] = q0.y; qv[2] = q0.z; qv[3] = q0.w; qv[4] = q1.x; qv[5] = q1.y; qv[6] = q1.z; qv[7] = q1.w;
+							} else
+#pragma unroll
+								for (int e8 = 0; e8 < 8; e8++) qv[e8] = c + e8 < d ? qh[u * d + c + e8] : 0.f;
+#pragma unroll
+							for (int kq = 0; kq < 4; kq++)
+#pragma unroll
+								for (int e8 = 0; e8 < 8; e8++) acc[kq][u] = fmaf(qv[e8], kk[kq][e8], acc[kq][u]);
+						}
+				}
+				float mine = 0.f; // lane kq * 4 + u keeps the sum of (key kq, head u)
+#pragma unroll
+				for (int kq = 0; kq < 4; kq++)
+#pragma unroll
+					for (int u = 0; u < 4; u++) {
+						const float tot = warp_sum(acc[kq][u]);
+						if (lane == kq * 4 + u) mine = tot;
+					}
+				if (lane < 16) {
+					const int kq = lane >> 2, u = lane & 3, jj = warp + kq * 8, j = j0 + jj;
+					if (u < nh) {
+						const int h = g * rep + hr + u;
+						float sv = 0.f;
+						if (jj < nb) {
+							sv = mine * a.scale;
+							if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+							if (a.r1) sv -= a.r1[h] * log1pf(a.r2[h] * (float) (i - j));
+						}
+						sc[h * SWA_KB + jj] = sv;
 					}
 				}
-		}
+			}
 		__syncthreads();
 		// mix the heads' scores
 		for (int x = tid; x < H * SWA_KB; x += nth) {
@@ -523,11 +551,15 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 				float acc[4];
 #pragma unroll
 				for (int u = 0; u < 4; u++) acc[u] = u < nh ? O[(size_t) (h0 + u) * dv + c] * alpha[h0 + u] : 0.f;
-				for (int jj = 0; jj < nb; jj++) {
-					const float v = ldf(vcol + (size_t) ((j0 + jj) % a.ring) * (G * dv));
+				for (int jb8 = 0; jb8 < nb; jb8 += 8) { // eight loads in flight
+					float v[8];
 #pragma unroll
-					for (int u = 0; u < 4; u++)
-						if (u < nh) acc[u] = fmaf(pr[(h0 + u) * SWA_KB + jj], v, acc[u]);
+					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) ((j0 + jb8 + e8) % a.ring) * (G * dv)) : 0.f;
+#pragma unroll
+					for (int e8 = 0; e8 < 8; e8++)
+#pragma unroll
+						for (int u = 0; u < 4; u++)
+							if (u < nh) acc[u] = fmaf(pr[(h0 + u) * SWA_KB + jb8 + e8], v[e8], acc[u]);
 				}
 #pragma unroll
 				for (int u = 0; u < 4; u++)

@@ -123,6 +123,8 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	float* h_logits = nullptr; // pinned, chunk x vocab
 	size_t proj_ld = 0;
 	cudaStream_t stream = nullptr, own_stream = nullptr;
+	cudaStream_t side = nullptr;                  // the recurrence of a layer runs here, beside the attention on `stream`
+	cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 	cudaGraphExec_t graph[2] = {nullptr, nullptr};
 	int pos = 0; // tokens the running sequence holds
 	int last_launches = 0;
@@ -382,19 +384,28 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		sa.step = m->d_step; sa.out = m->att;
 		sa.n_splits = 0; // the launcher spreads the keys over CTAs when the step has few tokens
 		sa.part_o = m->part_o; sa.part_ml = m->part_ml; sa.part_cap = m->part_cap; sa.tickets = m->tickets;
-		int swa_launches = 1;
-		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s, &swa_launches));
-		*nl += swa_launches;
 		Hgrn2Args ha = {};
 		ha.proj = m->proj; ha.ld = (int) m->proj_ld; ha.q_off = L.off_rq; ha.f_off = L.off_rf; ha.v_off = L.off_rv;
 		ha.H = Hr; ha.d = dr; ha.dv = dvr;
 		ha.f_bias = L.fb; ha.lower = L.lower; ha.norm_w = L.rnorm; ha.eps = m->eps;
 		ha.state = L.state; ha.step = m->d_step; ha.out = m->ro; ha.max_rows = m->chunk; ha.activated = 1;
-		XALM_TRY(launch_hgrn2(ha, s));
+		// the two mixers read the same projections and write different buffers: the recurrence runs on the side stream (a branch
+		// of the graph, when the step is captured) while the attention and its output projection run here
+		const bool overlap = tune("seq_overlap") != 0;
+		if (overlap) {
+			XALM_CUDA_CHECK(cudaEventRecord(m->ev_fork, s));
+			XALM_CUDA_CHECK(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
+		}
+		XALM_TRY(launch_hgrn2(ha, overlap ? m->side : s));
 		(*nl)++;
+		if (overlap) XALM_CUDA_CHECK(cudaEventRecord(m->ev_join, m->side));
+		int swa_launches = 1;
+		XALM_TRY(launch_swa(sa, n, m->precision == XALM_PRECISION_F32, s, &swa_launches));
+		*nl += swa_launches;
 		RowsEpi est;
 		est.kind = EPI_STORE; est.out = m->ol; est.ldo = W;
 		XALM_TRY(rows_product(m, m->att, H * dv, L.w_lo, &L.t_lo, n, W, H * dv, est, nl));
+		if (overlap) XALM_CUDA_CHECK(cudaStreamWaitEvent(s, m->ev_join, 0));
 		est.out = m->orr;
 		XALM_TRY(rows_product(m, m->ro, Hr * dvr, L.w_ro, &L.t_ro, n, W, Hr * dvr, est, nl));
 		dual_norm_hc_kernel<<<n, rt, 33 * 4, s>>>(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0));
@@ -525,6 +536,9 @@ void nb_destroy(Nb* m) {
 	tc_weight_free(&m->t_head);
 	if (m->h_logits) cudaFreeHost(m->h_logits);
 	if (m->own_stream) cudaStreamDestroy(m->own_stream);
+	if (m->side) cudaStreamDestroy(m->side);
+	if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+	if (m->ev_join) cudaEventDestroy(m->ev_join);
 	delete m;
 }
 
@@ -545,6 +559,9 @@ int nb_create(const char* json, int device, int max_tokens, int precision, Nb** 
 	if (device < 0 || device >= ndev) { delete m; return set_error(XALM_ERR_CUDA, "device %d not available (%d devices)", device, ndev); }
 	e = cudaSetDevice(device);
 	if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking);
+	if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking);
+	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming);
+	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming);
 	if (e != cudaSuccess) { delete m; return set_error(XALM_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e)); }
 	m->stream = m->own_stream;
 	*out = m;
