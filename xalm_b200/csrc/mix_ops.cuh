@@ -98,23 +98,52 @@ static __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_
 	extern __shared__ float sm[];
 	float* u = sm;            // width
 	float* red = sm + width;  // 33
-	const int t = blockIdx.x;
+	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x;
+	// Four columns per thread at a time, every load of the four issued before the first use: a one-token step runs one CTA of this
+	// kernel, and its time is the number of dependent trips to memory.
+	float av[MAX_STREAMS];
+#pragma unroll
+	for (int s = 0; s < MAX_STREAMS; s++) av[s] = (a && s < S) ? a[s] : 1.f;
 	float ss = 0.f;
-	for (int c = threadIdx.x; c < width; c += blockDim.x) {
-		float v = 0.f;
-		for (int s = 0; s < S; s++) {
-			const float x = xs[(size_t) s * stream_stride + (size_t) t * width + c];
-			v = a ? fmaf(a[s], x, v) : v + x;
+	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
+		float x[4][MAX_STREAMS];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+#pragma unroll
+			for (int s = 0; s < MAX_STREAMS; s++) x[k][s] = (s < S && c < width) ? xs[(size_t) s * stream_stride + (size_t) t * width + c] : 0.f;
 		}
-		u[c] = v;
-		ss = fmaf(v, v, ss);
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			float v = 0.f;
+#pragma unroll
+			for (int s = 0; s < MAX_STREAMS; s++)
+				if (s < S) v = a ? fmaf(av[s], x[k][s], v) : v + x[k][s];
+			if (c < width) {
+				u[c] = v;
+				ss = fmaf(v, v, ss);
+			}
+		}
 	}
 	const float tot = block_sum(ss, red);
 	const float r = 1.f / sqrtf(tot / (float) width + eps);
-	for (int c = threadIdx.x; c < width; c += blockDim.x) {
-		const float v = u[c];
-		if (h) h[(size_t) t * width + c] = v * r * (one_plus ? 1.f + w[c] : w[c]);
-		if (sum_out) sum_out[(size_t) t * width + c] = v;
+	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
+		float wv[4];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			wv[k] = (h && c < width) ? w[c] : 0.f;
+		}
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			if (c < width) {
+				const float v = u[c];
+				if (h) h[(size_t) t * width + c] = v * r * (one_plus ? 1.f + wv[k] : wv[k]);
+				if (sum_out) sum_out[(size_t) t * width + c] = v;
+			}
+		}
 	}
 }
 
@@ -366,44 +395,50 @@ struct SwaArgs {
 constexpr int SWA_KB = 32; // keys per block
 
 // joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
-__device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
-	const int H = a.H, dv = a.dv, ns = a.n_splits;
-	for (int x = tid; x < rows * H * dv; x += nth) {
-		const int t = t_first + x / (H * dv), hc = x % (H * dv), h = hc / dv;
-		const float* pml0 = a.part_ml + (size_t) t * ns * (H * 2) + 2 * h;
-		const float* po0 = a.part_o + (size_t) t * ns * (H * dv) + hc;
-		float m = -INFINITY;
-		for (int s0 = 0; s0 < ns; s0 += 8) { // eight loads in flight
-			float ms[8];
+__device__ __forceinline__ void swa_merge_one(const SwaArgs& a, int t, int hc) {
+	const int H = a.H, dv = a.dv, ns = a.n_splits, h = hc / dv;
+	const float* pml0 = a.part_ml + (size_t) t * ns * (H * 2) + 2 * h;
+	const float* po0 = a.part_o + (size_t) t * ns * (H * dv) + hc;
+	float m = -INFINITY, num = 0.f, den = 0.f;
+	for (int s0 = 0; s0 < ns; s0 += 8) { // eight splits' loads in flight, then one rescale for the eight
+		float ms[8], ls[8], os[8];
 #pragma unroll
-			for (int u = 0; u < 8; u++) ms[u] = s0 + u < ns ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2)) : -INFINITY;
-#pragma unroll
-			for (int u = 0; u < 8; u++) m = fmaxf(m, ms[u]);
+		for (int u = 0; u < 8; u++) {
+			const bool in = s0 + u < ns;
+			ms[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2)) : -INFINITY;
+			ls[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2) + 1) : 0.f;
+			os[u] = in ? __ldcg(po0 + (size_t) (s0 + u) * (H * dv)) : 0.f;
 		}
-		float num = 0.f, den = 0.f;
-		for (int s0 = 0; s0 < ns; s0 += 8) {
-			float ms[8], ls[8], os[8];
+		float mb = m;
 #pragma unroll
-			for (int u = 0; u < 8; u++) {
-				const bool in = s0 + u < ns;
-				ms[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2)) : -INFINITY;
-				ls[u] = in ? __ldcg(pml0 + (size_t) (s0 + u) * (H * 2) + 1) : 0.f;
-				os[u] = in ? __ldcg(po0 + (size_t) (s0 + u) * (H * dv)) : 0.f;
+		for (int u = 0; u < 8; u++) mb = fmaxf(mb, ms[u]);
+		if (mb == -INFINITY) continue;
+		const float keep = m == -INFINITY ? 0.f : expf(m - mb);
+		num *= keep;
+		den *= keep;
+		m = mb;
+#pragma unroll
+		for (int u = 0; u < 8; u++)
+			if (ms[u] != -INFINITY) {
+				const float w = expf(ms[u] - m);
+				num = fmaf(w, os[u], num);
+				den = fmaf(w, ls[u], den);
 			}
-#pragma unroll
-			for (int u = 0; u < 8; u++)
-				if (ms[u] != -INFINITY) {
-					const float w = expf(ms[u] - m);
-					num = fmaf(w, os[u], num);
-					den = fmaf(w, ls[u], den);
-				}
-		}
-		float o = num / den;
-		if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
-		a.out[(size_t) t * (H * dv) + hc] = o;
 	}
+	float o = num / den;
+	if (a.gate) o *= sigmoidf_(a.gate[(size_t) t * a.ldg + a.g_off + hc]);
+	a.out[(size_t) t * (H * dv) + hc] = o;
 }
-static __global__ void swa_merge_kernel(SwaArgs a) { swa_merge_rows(a, blockIdx.x, 1, threadIdx.x, blockDim.x); }
+__device__ __forceinline__ void swa_merge_rows(const SwaArgs& a, int t_first, int rows, int tid, int nth) {
+	const int hdv = a.H * a.dv;
+	for (int x = tid; x < rows * hdv; x += nth) swa_merge_one(a, t_first + x / hdv, x % hdv);
+}
+// grid (rows, ceil(H dv / 128)), 128 threads: a thread per output value, so that a one-token step's join is spread over many SMs
+static __global__ void swa_merge_kernel(SwaArgs a) {
+	const int hc = blockIdx.y * blockDim.x + threadIdx.x;
+	if (hc < a.H * a.dv) swa_merge_one(a, blockIdx.x, hc);
+}
+
 // With key splits and a ticket counter per query tile: the split that arrives last joins the parts of the tile's rows and leaves the
 // counter at zero for the next launch.  Every thread of the CTA calls it after writing its parts.
 __device__ __forceinline__ void swa_join_last(const SwaArgs& a, int tile, int t_first, int rows, int tid, int nth) {
@@ -447,7 +482,11 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
 	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
 
-	for (int x = tid; x < H * d; x += nth) qs[x] = a.q[(size_t) t * a.ldq + a.q_off + x];
+	if (((a.ldq | a.q_off | (H * d)) & 3) == 0) {
+#pragma unroll 4
+		for (int x = tid * 4; x < H * d; x += nth * 4) *reinterpret_cast<float4*>(qs + x) = *reinterpret_cast<const float4*>(a.q + (size_t) t * a.ldq + a.q_off + x);
+	} else
+		for (int x = tid; x < H * d; x += nth) qs[x] = a.q[(size_t) t * a.ldq + a.q_off + x];
 	for (int x = tid; x < H * H; x += nth) tk[x] = a.talk ? a.talk[x] : (x / H == x % H ? 1.f : 0.f);
 	for (int x = tid; x < H; x += nth) { mrun[x] = -INFINITY; lrun[x] = 0.f; }
 	for (int x = tid; x < H * dv; x += nth) O[x] = 0.f;
@@ -579,7 +618,6 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 		float* pml = a.part_ml + ((size_t) t * a.n_splits + sp) * (H * 2);
 		for (int x = tid; x < H * dv; x += nth) po[x] = O[x];
 		for (int x = tid; x < H; x += nth) { pml[2 * x] = mrun[x]; pml[2 * x + 1] = lrun[x]; }
-		if (a.tickets) swa_join_last(a, blockIdx.x, t, 1, tid, nth);
 	}
 }
 
@@ -1076,19 +1114,65 @@ inline size_t hgrn2_cols_smem_bytes(int dpl, int warps, int max_rows) {
 static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
                                     float eps, int width, RowsEpi e) {
 	extern __shared__ float sm[];
+	__shared__ float hm[MAX_STREAMS * MAX_STREAMS], ho[MAX_STREAMS];
 	float* red = sm;
-	const int t = blockIdx.x;
+	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, S = e.S;
+	if (tid < S * S) hm[tid] = e.hmix ? e.hmix[tid] : (tid / S == tid % S ? 1.f : 0.f);
+	if (tid < S) ho[tid] = e.hout ? e.hout[tid] : 1.f;
+	// four columns per thread at a time, loads first (see hc_norm_kernel)
 	float sa = 0.f, sb = 0.f;
-	for (int c = threadIdx.x; c < width; c += blockDim.x) {
-		const float x = A[(size_t) t * width + c], y = B[(size_t) t * width + c];
-		sa = fmaf(x, x, sa);
-		sb = fmaf(y, y, sb);
+	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
+		float x[4], y[4];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			x[k] = c < width ? A[(size_t) t * width + c] : 0.f;
+			y[k] = c < width ? B[(size_t) t * width + c] : 0.f;
+		}
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			sa = fmaf(x[k], x[k], sa);
+			sb = fmaf(y[k], y[k], sb);
+		}
 	}
 	const float ra = 1.f / sqrtf(block_sum(sa, red) / (float) width + eps);
-	const float rb = 1.f / sqrtf(block_sum(sb, red) / (float) width + eps);
-	for (int c = threadIdx.x; c < width; c += blockDim.x) {
-		const float y = 0.5f * (A[(size_t) t * width + c] * ra * wa[c] + B[(size_t) t * width + c] * rb * wb[c]);
-		hc_write(e, t, c, width, y);
+	const float rb = 1.f / sqrtf(block_sum(sb, red) / (float) width + eps); // block_sum's barriers also publish hm / ho
+	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
+		float x[4], y[4], wx[4], wy[4], sc[4], old[4][MAX_STREAMS];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			const bool in = c < width;
+			x[k] = in ? A[(size_t) t * width + c] : 0.f;
+			y[k] = in ? B[(size_t) t * width + c] : 0.f;
+			wx[k] = in ? wa[c] : 0.f;
+			wy[k] = in ? wb[c] : 0.f;
+			sc[k] = (in && e.scale) ? e.scale[c] : 1.f;
+#pragma unroll
+			for (int s = 0; s < MAX_STREAMS; s++) old[k][s] = (in && s < S) ? e.xs[(size_t) s * e.stream_stride + (size_t) t * width + c] : 0.f;
+		}
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			if (c >= width) continue;
+			const float v = 0.5f * (x[k] * ra * wx[k] + y[k] * rb * wy[k]);
+			const float yv = e.scale ? sc[k] * v : v;
+#pragma unroll
+			for (int q = 0; q < MAX_STREAMS; q++)
+				if (q < S) {
+					float acc = 0.f;
+					if (e.hmix) {
+#pragma unroll
+						for (int s2 = 0; s2 < MAX_STREAMS; s2++)
+							if (s2 < S) acc = fmaf(hm[s2 * S + q], old[k][s2], acc);
+					} else {
+#pragma unroll
+						for (int s2 = 0; s2 < MAX_STREAMS; s2++)
+							if (s2 == q) acc = old[k][s2];
+					}
+					e.xs[(size_t) q * e.stream_stride + (size_t) t * width + c] = fmaf(ho[q], yv, acc);
+				}
+		}
 	}
 }
 
@@ -1195,6 +1279,7 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		want = (int) std::min<long long>(want, std::max<long long>(1, tq ? keys / (2 * SWA_KB) : (keys + SWA_KB - 1) / SWA_KB)); // key blocks per CTA: >= 2 (tiled), 1 (one query)
 		a.n_splits = (a.part_o && a.part_ml) ? std::max(1, std::min(want, a.part_cap / std::max(1, rows))) : 1;
 	}
+	if (!tq) a.tickets = nullptr; // the one-query kernel's parts are joined by a kernel of many CTAs: one CTA would take longer than the attention
 	if (launches) *launches = a.n_splits > 1 && !a.tickets ? 2 : 1;
 	if (tq) {
 		a.tq = tq;
@@ -1214,7 +1299,7 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 	}
 	XALM_TRY(launch_check("swa_attn"));
 	if (a.n_splits > 1 && !a.tickets) {
-		swa_merge_kernel<<<rows, 256, 0, s>>>(a);
+		swa_merge_kernel<<<dim3(rows, (a.H * a.dv + 127) / 128), 128, 0, s>>>(a);
 		XALM_TRY(launch_check("swa_merge"));
 	}
 	return XALM_OK;
