@@ -386,6 +386,8 @@ struct SwaArgs {
 	int n_splits;      // > 1: partial results to part_*; swa_merge_kernel finishes.  0: the launcher chooses (part_cap bounds it)
 	int part_cap;      // (row, split) pairs part_o / part_ml have room for (only read when n_splits == 0)
 	int tq;            // queries per CTA of the tiled kernel (set by the launcher)
+	int stage_off;     // one-query kernel: > 0: the key block's K and V rows are copied (cp.async, 16 bytes) to shared memory at this float offset
+	                   // before they are used, so that a CTA's time is a few trips to memory (set by the launcher)
 	unsigned* tickets; // one zeroed counter per query tile, or NULL.  With it the tiled kernel's last-arriving key split joins the parts itself
 	                   // (and resets the counter); without it swa_merge_kernel follows
 	float* part_o;     // (T, n_splits, H * dv)
@@ -481,6 +483,26 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	int per = (nk + a.n_splits - 1) / a.n_splits;
 	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
 	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
+	// staged rows: Ks[jj][G d], Vs[jj][G dv] in the cache's element type
+	const bool staged = a.stage_off > 0;
+	CT* Ks = reinterpret_cast<CT*>(sm + a.stage_off);
+	CT* Vs = Ks + (size_t) SWA_KB * G * d;
+	auto stage = [&](int j0, int nb) {
+		constexpr int EPC = 16 / (int) sizeof(CT); // elements per 16-byte copy
+		const int kch = G * d / EPC, vch = G * dv / EPC;
+		for (int x = tid; x < nb * kch; x += nth) {
+			const int jj = x / kch, c = (x % kch) * EPC;
+			const unsigned dst = (unsigned) __cvta_generic_to_shared(Ks + (size_t) jj * (G * d) + c);
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + c) : "memory");
+		}
+		for (int x = tid; x < nb * vch; x += nth) {
+			const int jj = x / vch, c = (x % vch) * EPC;
+			const unsigned dst = (unsigned) __cvta_generic_to_shared(Vs + (size_t) jj * (G * dv) + c);
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) ((j0 + jj) % a.ring) * (G * dv) + c) : "memory");
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	if (staged && jb < je) stage(jb, min(SWA_KB, je - jb)); // in flight while the query and the constants are read
 
 	if (((a.ldq | a.q_off | (H * d)) & 3) == 0) {
 #pragma unroll 4
@@ -494,6 +516,14 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 
 	for (int j0 = jb; j0 < je; j0 += SWA_KB) {
 		const int nb = min(SWA_KB, je - j0);
+		if (staged) {
+			if (j0 != jb) {
+				__syncthreads(); // the last reader of the staged rows is done
+				stage(j0, nb);
+			}
+			asm volatile("cp.async.wait_all;" ::: "memory");
+			__syncthreads();
+		}
 		// raw scores: a warp takes keys warp, warp + 8, ... of the block (four with 256 threads), its lanes along the channels, eight
 		// each; the loads of all four keys are issued before the first product, and up to four heads of the group share them.
 		// Then scale, soft cap, distance bias.
@@ -507,7 +537,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 #pragma unroll
 					for (int kq = 0; kq < 4; kq++) {
 						const int jj = warp + kq * 8;
-						const CT* kr = kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + g * d + c;
+						const CT* kr = (staged ? Ks + (size_t) jj * (G * d) : kc + (size_t) ((j0 + jj) % a.ring) * (G * d)) + g * d + c;
 						if (jj < nb && vec8) ld8(kr, kk[kq]);
 						else
 #pragma unroll
@@ -584,7 +614,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 		// O <- alpha O + P V: a thread per value column of a kv group, up to four heads of the group per read of V
 		for (int x = tid; x < G * dv; x += nth) {
 			const int g = x / dv, c = x % dv;
-			const CT* vcol = vc + g * dv + c;
+			const CT* vcol = (staged ? Vs : vc) + g * dv + c;
 			for (int hr = 0; hr < rep; hr += 4) {
 				const int h0 = g * rep + hr, nh = min(4, rep - hr);
 				float acc[4];
@@ -593,7 +623,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 				for (int jb8 = 0; jb8 < nb; jb8 += 8) { // eight loads in flight
 					float v[8];
 #pragma unroll
-					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) ((j0 + jb8 + e8) % a.ring) * (G * dv)) : 0.f;
+					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) (staged ? jb8 + e8 : (j0 + jb8 + e8) % a.ring) * (G * dv)) : 0.f;
 #pragma unroll
 					for (int e8 = 0; e8 < 8; e8++)
 #pragma unroll
@@ -621,6 +651,9 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	}
 }
 
+// float offset of the staged rows behind the kernel's own arrays (16-byte aligned), and the bytes they take
+inline size_t swa_stage_off(int H, int d, int dv) { return ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv + 3) & ~(size_t) 3; }
+inline size_t swa_stage_bytes(int G, int d, int dv, bool cache_f32) { return (size_t) SWA_KB * G * (d + dv) * (cache_f32 ? 4 : 2); }
 inline size_t swa_smem_bytes(int H, int d, int dv) { return sizeof(float) * ((size_t) H * d + 2 * (size_t) H * SWA_KB + (size_t) H * H + 3 * (size_t) H + (size_t) H * dv); }
 
 
@@ -689,6 +722,54 @@ __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* bas
 	}
 }
 
+// raw scores of one kv group's rows against the staged K tile: 4 x KT register tiles (4 rows, KT keys 32 / KT apart), so that a
+// tile with few rows per group still has work for every thread; then scale, soft cap, distance bias -> Sc[key][row]
+template <int KT>
+__device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, const float* KV, float* Sc, int g, int Rg, int R, int ldq, int ldkv, int dp,
+                                             int TQ, int rep, int nq, int nbk, int i_lo, int j0, int tid, int nth) {
+	constexpr int NTK = SWA_KB / KT;
+	for (int tile = tid; tile < (Rg >> 2) * NTK; tile += nth) {
+		const int mt = tile / NTK, nt = tile % NTK;
+		const float* qp = Qs + (size_t) (g * Rg + 4 * mt) * ldq;
+		const float* kp = KV + nt * ldkv;
+		float acc[4][KT] = {};
+		for (int k = 0; k < dp; k += 4) {
+			float4 qv[4], kv[KT];
+#pragma unroll
+			for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(qp + i * ldq + k);
+#pragma unroll
+			for (int u = 0; u < KT; u++) kv[u] = *reinterpret_cast<const float4*>(kp + u * NTK * ldkv + k);
+#pragma unroll
+			for (int i = 0; i < 4; i++)
+#pragma unroll
+				for (int u = 0; u < KT; u++) {
+					acc[i][u] = fmaf(qv[i].x, kv[u].x, acc[i][u]);
+					acc[i][u] = fmaf(qv[i].y, kv[u].y, acc[i][u]);
+					acc[i][u] = fmaf(qv[i].z, kv[u].z, acc[i][u]);
+					acc[i][u] = fmaf(qv[i].w, kv[u].w, acc[i][u]);
+				}
+		}
+#pragma unroll
+		for (int u = 0; u < KT; u++) {
+			const int jj = nt + NTK * u, j = j0 + jj;
+			float o4[4];
+#pragma unroll
+			for (int i = 0; i < 4; i++) {
+				const int rr = 4 * mt + i, hr = rr / TQ, q = rr % TQ;
+				float s = 0.f;
+				if (hr < rep && q < nq && jj < nbk) {
+					const int h = g * rep + hr;
+					s = acc[i][u] * a.scale;
+					if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
+					if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) max(i_lo + q - j, 0));
+				}
+				o4[i] = s;
+			}
+			*reinterpret_cast<float4*>(Sc + (size_t) jj * R + g * Rg + 4 * mt) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+		}
+	}
+}
+
 template <typename CT>
 __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 	extern __shared__ __align__(16) float sm[];
@@ -696,6 +777,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 	const SwaTile z = swa_tile_dims(H, G, d, dv, TQ);
 	const int Rg = z.Rg, R = z.R, dp = z.dp, ldq = z.ldq, dvp = z.dvp, Hp = z.Hp;
 	const int ldkv = ldq > dvp ? ldq : dvp;
+	const int kt = (Rg >> 2) * 8 >= (int) blockDim.x ? 4 : (Rg >> 2) * 16 >= (int) blockDim.x ? 2 : 1; // keys per thread of the score tiles
 	float* Qs = sm;                          // R * ldq
 	float* KV = Qs + (size_t) R * ldq;       // SWA_KB * ldkv: one group's K tile, later its V tile
 	float* Sc = KV + (size_t) SWA_KB * ldkv; // SWA_KB * R raw scores
@@ -747,46 +829,9 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
 			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, a.ring, tid, nth);
 			__syncthreads();
-			for (int tile = tid; tile < (Rg >> 2) * 8; tile += nth) {
-				const int mt = tile >> 3, nt = tile & 7;
-				const float* qp = Qs + (size_t) (g * Rg + 4 * mt) * ldq;
-				const float* kp = KV + nt * ldkv;
-				float acc[4][4] = {};
-				for (int k = 0; k < dp; k += 4) {
-					float4 qv[4], kv[4];
-#pragma unroll
-					for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(qp + i * ldq + k);
-#pragma unroll
-					for (int u = 0; u < 4; u++) kv[u] = *reinterpret_cast<const float4*>(kp + u * 8 * ldkv + k);
-#pragma unroll
-					for (int i = 0; i < 4; i++)
-#pragma unroll
-						for (int u = 0; u < 4; u++) {
-							acc[i][u] = fmaf(qv[i].x, kv[u].x, acc[i][u]);
-							acc[i][u] = fmaf(qv[i].y, kv[u].y, acc[i][u]);
-							acc[i][u] = fmaf(qv[i].z, kv[u].z, acc[i][u]);
-							acc[i][u] = fmaf(qv[i].w, kv[u].w, acc[i][u]);
-						}
-				}
-#pragma unroll
-				for (int u = 0; u < 4; u++) {
-					const int jj = nt + 8 * u, j = j0 + jj;
-					float o4[4];
-#pragma unroll
-					for (int i = 0; i < 4; i++) {
-						const int rr = 4 * mt + i, hr = rr / TQ, q = rr % TQ;
-						float s = 0.f;
-						if (hr < rep && q < nq && jj < nbk) {
-							const int h = g * rep + hr;
-							s = acc[i][u] * a.scale;
-							if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-							if (a.r1) s -= a.r1[h] * log1pf(a.r2[h] * (float) max(i_lo + q - j, 0));
-						}
-						o4[i] = s;
-					}
-					*reinterpret_cast<float4*>(Sc + (size_t) jj * R + g * Rg + 4 * mt) = make_float4(o4[0], o4[1], o4[2], o4[3]);
-				}
-			}
+			if (kt == 4) swa_qk_tiles<4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			else if (kt == 2) swa_qk_tiles<2>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			else swa_qk_tiles<1>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
 		}
 		__syncthreads();
 		// ---- mix the heads' scores (4 output heads per thread), mask ----
@@ -1224,9 +1269,10 @@ static inline int hc_norm_prepare(int width) {
 	}
 	return XALM_OK;
 }
-static inline int swa_prepare(int H, int d, int dv) {
+static inline int swa_prepare(int H, int d, int dv) { // before any launch (and outside a stream capture): the kernels may ask for up to 200 KB
 	static bool raised = false;
-	if (swa_smem_bytes(H, d, dv) > 48 * 1024 && !raised) {
+	(void) H; (void) d; (void) dv;
+	if (!raised) {
 		XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 		XALM_CUDA_CHECK(cudaFuncSetAttribute(swa_attn_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 		raised = true;
@@ -1292,7 +1338,13 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 		if (cache_f32) swa_tile_kernel<float><<<grid, 256, smem, s>>>(a);
 		else swa_tile_kernel<__nv_bfloat16><<<grid, 256, smem, s>>>(a);
 	} else {
-		const size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
+		size_t smem = swa_smem_bytes(a.H, a.d, a.dv);
+		const size_t staged = swa_stage_off(a.H, a.d, a.dv) * 4 + swa_stage_bytes(a.G, a.d, a.dv, cache_f32);
+		a.stage_off = 0;
+		if (((a.d | a.dv) & 7) == 0 && staged <= 200 * 1024) { // rows of whole 16-byte pieces, and room for a key block
+			a.stage_off = (int) swa_stage_off(a.H, a.d, a.dv);
+			smem = staged;
+		}
 		XALM_TRY(swa_prepare(a.H, a.d, a.dv));
 		if (cache_f32) swa_attn_kernel<float><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
 		else swa_attn_kernel<__nv_bfloat16><<<dim3(rows, a.n_splits), 256, smem, s>>>(a);
