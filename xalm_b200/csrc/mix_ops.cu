@@ -171,8 +171,7 @@ int xalm_cuda_dual_norm_hyper(float* xs, const float* a, const float* b, const f
 	e.scale = pool.put(scale, (size_t) W);
 	const float *d_a = pool.put(a, (size_t) T * W), *d_b = pool.put(b, (size_t) T * W), *d_wa = pool.put(wa, (size_t) W), *d_wb = pool.put(wb, (size_t) W);
 	if (!e.xs || !d_a || !d_b || !d_wa || !d_wb) return set_error(XALM_ERR_CUDA, "dual_norm_hyper: device allocation failed");
-	const int rt = std::min(256, std::max(32, (W + 31) / 32 * 32));
-	dual_norm_hc_kernel<<<T, rt, 33 * 4>>>(d_a, d_b, d_wa, d_wb, eps, W, e);
+	XALM_TRY(launch_dual_norm_hc(d_a, d_b, d_wa, d_wb, eps, W, e, T, 0));
 	XALM_TRY(finish("dual_norm_hyper"));
 	XALM_CUDA_CHECK(cudaMemcpy(xs, e.xs, (size_t) S * T * W * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;

@@ -93,7 +93,9 @@ __global__ void embed_streams_kernel(const WT* __restrict__ table, const int* __
 // ---- hyper-connection read + RMS norm -------------------------------------------------------------------------------------
 // h[t] = rmsnorm(sum_s a[s] xs[s][t]) * (one_plus ? 1 + w : w).  a == nullptr: every coefficient is 1 (the final sum of streams).
 // `sum_out` (optional) receives the un-normed combination (the residual stream as a reader outside the model sees it).
-static __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t stream_stride, const float* __restrict__ a, const float* __restrict__ w,
+// SS: the most streams this instance takes (its loops are unrolled to SS: the code of a one-CTA launch should be short to fetch)
+template <int SS>
+__global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t stream_stride, const float* __restrict__ a, const float* __restrict__ w,
                                int one_plus, float eps, int width, float* __restrict__ h, float* __restrict__ sum_out) {
 	extern __shared__ float sm[];
 	float* u = sm;            // width
@@ -101,24 +103,24 @@ static __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_
 	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x;
 	// Four columns per thread at a time, every load of the four issued before the first use: a one-token step runs one CTA of this
 	// kernel, and its time is the number of dependent trips to memory.
-	float av[MAX_STREAMS];
+	float av[SS];
 #pragma unroll
-	for (int s = 0; s < MAX_STREAMS; s++) av[s] = (a && s < S) ? a[s] : 1.f;
+	for (int s = 0; s < SS; s++) av[s] = (a && s < S) ? a[s] : 1.f;
 	float ss = 0.f;
 	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
-		float x[4][MAX_STREAMS];
+		float x[4][SS];
 #pragma unroll
 		for (int k = 0; k < 4; k++) {
 			const int c = c0 + k * nth + tid;
 #pragma unroll
-			for (int s = 0; s < MAX_STREAMS; s++) x[k][s] = (s < S && c < width) ? xs[(size_t) s * stream_stride + (size_t) t * width + c] : 0.f;
+			for (int s = 0; s < SS; s++) x[k][s] = (s < S && c < width) ? xs[(size_t) s * stream_stride + (size_t) t * width + c] : 0.f;
 		}
 #pragma unroll
 		for (int k = 0; k < 4; k++) {
 			const int c = c0 + k * nth + tid;
 			float v = 0.f;
 #pragma unroll
-			for (int s = 0; s < MAX_STREAMS; s++)
+			for (int s = 0; s < SS; s++)
 				if (s < S) v = a ? fmaf(av[s], x[k][s], v) : v + x[k][s];
 			if (c < width) {
 				u[c] = v;
@@ -1156,13 +1158,14 @@ inline size_t hgrn2_cols_smem_bytes(int dpl, int warps, int max_rows) {
 }
 
 // ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
-static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
+template <int SS>
+__global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
                                     float eps, int width, RowsEpi e) {
 	extern __shared__ float sm[];
 	__shared__ float hm[MAX_STREAMS * MAX_STREAMS], ho[MAX_STREAMS];
 	float* red = sm;
 	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, S = e.S;
-	if (tid < S * S) hm[tid] = e.hmix ? e.hmix[tid] : (tid / S == tid % S ? 1.f : 0.f);
+	for (int x = tid; x < S * S; x += nth) hm[x] = e.hmix ? e.hmix[x] : (x / S == x % S ? 1.f : 0.f);
 	if (tid < S) ho[tid] = e.hout ? e.hout[tid] : 1.f;
 	// four columns per thread at a time, loads first (see hc_norm_kernel)
 	float sa = 0.f, sb = 0.f;
@@ -1183,7 +1186,7 @@ static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const fl
 	const float ra = 1.f / sqrtf(block_sum(sa, red) / (float) width + eps);
 	const float rb = 1.f / sqrtf(block_sum(sb, red) / (float) width + eps); // block_sum's barriers also publish hm / ho
 	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
-		float x[4], y[4], wx[4], wy[4], sc[4], old[4][MAX_STREAMS];
+		float x[4], y[4], wx[4], wy[4], sc[4], old[4][SS];
 #pragma unroll
 		for (int k = 0; k < 4; k++) {
 			const int c = c0 + k * nth + tid;
@@ -1194,7 +1197,7 @@ static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const fl
 			wy[k] = in ? wb[c] : 0.f;
 			sc[k] = (in && e.scale) ? e.scale[c] : 1.f;
 #pragma unroll
-			for (int s = 0; s < MAX_STREAMS; s++) old[k][s] = (in && s < S) ? e.xs[(size_t) s * e.stream_stride + (size_t) t * width + c] : 0.f;
+			for (int s = 0; s < SS; s++) old[k][s] = (in && s < S) ? e.xs[(size_t) s * e.stream_stride + (size_t) t * width + c] : 0.f;
 		}
 #pragma unroll
 		for (int k = 0; k < 4; k++) {
@@ -1203,16 +1206,16 @@ static __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const fl
 			const float v = 0.5f * (x[k] * ra * wx[k] + y[k] * rb * wy[k]);
 			const float yv = e.scale ? sc[k] * v : v;
 #pragma unroll
-			for (int q = 0; q < MAX_STREAMS; q++)
+			for (int q = 0; q < SS; q++)
 				if (q < S) {
 					float acc = 0.f;
 					if (e.hmix) {
 #pragma unroll
-						for (int s2 = 0; s2 < MAX_STREAMS; s2++)
+						for (int s2 = 0; s2 < SS; s2++)
 							if (s2 < S) acc = fmaf(hm[s2 * S + q], old[k][s2], acc);
 					} else {
 #pragma unroll
-						for (int s2 = 0; s2 < MAX_STREAMS; s2++)
+						for (int s2 = 0; s2 < SS; s2++)
 							if (s2 == q) acc = old[k][s2];
 					}
 					e.xs[(size_t) q * e.stream_stride + (size_t) t * width + c] = fmaf(ho[q], yv, acc);
@@ -1264,7 +1267,10 @@ static inline int launch_rows(const float* A, int lda, const void* W, bool w_bf1
 static inline int hc_norm_prepare(int width) {
 	static bool raised = false;
 	if ((size_t) (width + 33) * 4 > 48 * 1024 && !raised) {
-		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(hc_norm_kernel<MAX_STREAMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 		raised = true;
 	}
 	return XALM_OK;
@@ -1298,8 +1304,22 @@ static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, c
                           float* sum_out, int rows, cudaStream_t s) {
 	const size_t smem = (size_t) (width + 33) * 4;
 	XALM_TRY(hc_norm_prepare(width));
-	hc_norm_kernel<<<rows, norm_threads(width), smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
+	const int nt = norm_threads(width);
+	if (S <= 1) hc_norm_kernel<1><<<rows, nt, smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
+	else if (S <= 2) hc_norm_kernel<2><<<rows, nt, smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
+	else if (S <= 4) hc_norm_kernel<4><<<rows, nt, smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
+	else hc_norm_kernel<MAX_STREAMS><<<rows, nt, smem, s>>>(xs, S, stream_stride, a, w, one_plus, eps, width, h, sum_out);
 	return launch_check("hc_norm");
+}
+
+static inline int launch_dual_norm_hc(const float* A, const float* B, const float* wa, const float* wb, float eps, int width, const RowsEpi& e, int rows,
+                                      cudaStream_t s) {
+	const int nt = norm_threads(width);
+	if (e.S <= 1) dual_norm_hc_kernel<1><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
+	else if (e.S <= 2) dual_norm_hc_kernel<2><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
+	else if (e.S <= 4) dual_norm_hc_kernel<4><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
+	else dual_norm_hc_kernel<MAX_STREAMS><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
+	return launch_check("dual_norm_hc");
 }
 
 // Queries per CTA of the tiled kernel: the most (<= 16, <= rows rounded up to a power of two) whose tile leaves room for two CTAs

@@ -408,8 +408,8 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		if (overlap) XALM_CUDA_CHECK(cudaStreamWaitEvent(s, m->ev_join, 0));
 		est.out = m->orr;
 		XALM_TRY(rows_product(m, m->ro, Hr * dvr, L.w_ro, &L.t_ro, n, W, Hr * dvr, est, nl));
-		dual_norm_hc_kernel<<<n, rt, 33 * 4, s>>>(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0));
-		NB_LAUNCH_CHECK("dual_norm_hc");
+		XALM_TRY(launch_dual_norm_hc(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0), n, s));
+		(*nl)++;
 		// ---- feed-forward ----
 		if (L.has_mlp) {
 			XALM_TRY(launch_hc_norm(m->xs, S, sstride, L.hc_in[1], L.norm2, 1, m->eps, W, m->h, nullptr, n, s));
