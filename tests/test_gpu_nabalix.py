@@ -162,7 +162,11 @@ LAYER_A = dict(H=4, G=2, d=8, dv=12, window=9, softcap=6.0, Hr=2, dr=8, dvr=6, f
 LAYER_B = dict(H=3, G=3, d=16, dv=8, window=21, softcap=4.0, Hr=1, dr=4, dvr=24, ff=None)
 LAYER_C = dict(H=2, G=1, d=4, dv=4, window=5, scale=0.9, softcap=2.0, Hr=3, dr=5, dvr=7, ff=40, limit=3.0)
 LAYER_T = dict(H=4, G=2, d=8, dv=16, window=19, softcap=5.0, Hr=2, dr=6, dvr=32, ff=128, limit=1.5)   # every product a whole number of 64-wide K tiles
+LAYER_W = dict(H=12, G=2, d=40, dv=24, window=1, softcap=8.0, Hr=5, dr=24, dvr=200, ff=None)             # six query heads per kv head, a window of one
+LAYER_X = dict(H=16, G=2, d=16, dv=32, window=200, softcap=5.0, Hr=1, dr=130, dvr=8, ff=72, limit=0.5)   # eight per kv head, a window beyond the prompt
+LAYER_1 = dict(H=1, G=1, d=64, dv=8, window=2, softcap=1.0, Hr=1, dr=1, dvr=1, ff=8, limit=1.0)          # sizes of one
 CONFIGS = {
+    "wide_groups": O.make_config(vocab=130, width=80, streams=4, layers=[LAYER_W, LAYER_X, LAYER_1]),
     "k64_tiles": O.make_config(vocab=68, width=64, streams=2, layers=[LAYER_T, dict(LAYER_T, ff=None), LAYER_T]),
     "mixed3": O.make_config(vocab=67, width=48, streams=2, layers=[LAYER_A, LAYER_B, LAYER_C]),
     "one_stream": O.make_config(vocab=31, width=40, streams=1, layers=[LAYER_C, LAYER_A]),
