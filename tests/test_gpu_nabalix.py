@@ -50,10 +50,11 @@ def test_window_attention_op(H, G, d, dv, pos0, T, window, splits):
 
 @pytest.mark.parametrize("T,splits", [(5, 1), (1, 1), (1, 3)])
 @pytest.mark.parametrize("offset", [0, 1])
-def test_window_edge_stands_out(T, splits, offset):
+@pytest.mark.parametrize("dv", [4, 8])                       # 8: a one-token step copies its key block to shared memory first
+def test_window_edge_stands_out(T, splits, offset, dv):
     """One key carries a score far above the rest and a value nobody else has; it sits on the last visible place of the window
     (offset 0) or one further back (offset 1), for the last row of a prompt portion and for a token decoded alone."""
-    H, G, d, dv, window, pos0 = 2, 1, 8, 4, 24, 60
+    H, G, d, window, pos0 = 2, 1, 8, 24, 60
     n = pos0 + T
     i = n - 1
     target = i - (window - 1) - offset
@@ -73,8 +74,9 @@ def test_window_edge_stands_out(T, splits, offset):
         assert got[-2].min() > 90.0                          # the row before still sees it
 
 
-def test_window_far_key_among_hundreds():
-    H, G, d, dv, pos0, T = 2, 2, 8, 4, 700, 1
+@pytest.mark.parametrize("dv", [4, 16])
+def test_window_far_key_among_hundreds(dv):
+    H, G, d, pos0, T = 2, 2, 8, 700, 1
     n = pos0 + T
     rng = np.random.default_rng(3)
     k = 0.05 * rng.standard_normal((n, G * d))

@@ -724,25 +724,25 @@ __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* bas
 	}
 }
 
-// raw scores of one kv group's rows against the staged K tile: 4 x KT register tiles (4 rows, KT keys 32 / KT apart), so that a
+// raw scores of one kv group's rows against the staged K tile: RT x KT register tiles (RT rows, KT keys 32 / KT apart), so that a
 // tile with few rows per group still has work for every thread; then scale, soft cap, distance bias -> Sc[key][row]
-template <int KT>
+template <int KT, int RT>
 __device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, const float* KV, float* Sc, int g, int Rg, int R, int ldq, int ldkv, int dp,
                                              int TQ, int rep, int nq, int nbk, int i_lo, int j0, int tid, int nth) {
 	constexpr int NTK = SWA_KB / KT;
-	for (int tile = tid; tile < (Rg >> 2) * NTK; tile += nth) {
+	for (int tile = tid; tile < (Rg / RT) * NTK; tile += nth) {
 		const int mt = tile / NTK, nt = tile % NTK;
-		const float* qp = Qs + (size_t) (g * Rg + 4 * mt) * ldq;
+		const float* qp = Qs + (size_t) (g * Rg + RT * mt) * ldq;
 		const float* kp = KV + nt * ldkv;
-		float acc[4][KT] = {};
+		float acc[RT][KT] = {};
 		for (int k = 0; k < dp; k += 4) {
-			float4 qv[4], kv[KT];
+			float4 qv[RT], kv[KT];
 #pragma unroll
-			for (int i = 0; i < 4; i++) qv[i] = *reinterpret_cast<const float4*>(qp + i * ldq + k);
+			for (int i = 0; i < RT; i++) qv[i] = *reinterpret_cast<const float4*>(qp + i * ldq + k);
 #pragma unroll
 			for (int u = 0; u < KT; u++) kv[u] = *reinterpret_cast<const float4*>(kp + u * NTK * ldkv + k);
 #pragma unroll
-			for (int i = 0; i < 4; i++)
+			for (int i = 0; i < RT; i++)
 #pragma unroll
 				for (int u = 0; u < KT; u++) {
 					acc[i][u] = fmaf(qv[i].x, kv[u].x, acc[i][u]);
@@ -754,10 +754,10 @@ __device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, 
 #pragma unroll
 		for (int u = 0; u < KT; u++) {
 			const int jj = nt + NTK * u, j = j0 + jj;
-			float o4[4];
+			float o4[RT];
 #pragma unroll
-			for (int i = 0; i < 4; i++) {
-				const int rr = 4 * mt + i, hr = rr / TQ, q = rr % TQ;
+			for (int i = 0; i < RT; i++) {
+				const int rr = RT * mt + i, hr = rr / TQ, q = rr % TQ;
 				float s = 0.f;
 				if (hr < rep && q < nq && jj < nbk) {
 					const int h = g * rep + hr;
@@ -767,7 +767,44 @@ __device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, 
 				}
 				o4[i] = s;
 			}
-			*reinterpret_cast<float4*>(Sc + (size_t) jj * R + g * Rg + 4 * mt) = make_float4(o4[0], o4[1], o4[2], o4[3]);
+			float* sp = Sc + (size_t) jj * R + g * Rg + RT * mt;
+			if (RT == 4) *reinterpret_cast<float4*>(sp) = make_float4(o4[0], o4[1], o4[RT - 2], o4[RT - 1]);
+			else *reinterpret_cast<float2*>(sp) = make_float2(o4[0], o4[1]);
+		}
+	}
+}
+
+// O[row][:] <- alpha[row] O[row][:] + sum_key P[key][row] V[key][:] for one kv group's rows: 4 x CW register tiles (CW = 4 value columns, or 2
+// when that leaves threads without a tile)
+template <int CW>
+__device__ __forceinline__ void swa_pv_tiles(const float* Pr, const float* KV, float* O, const float* alpha, int g, int Rg, int R, int ldkv, int dvp, int tid, int nth) {
+	const int NTv = dvp / CW;
+	for (int tile = tid; tile < (Rg >> 2) * NTv; tile += nth) {
+		const int mt = tile / NTv, nt = tile % NTv, rb = g * Rg + 4 * mt;
+		float acc[4][CW] = {};
+#pragma unroll 8
+		for (int jj = 0; jj < SWA_KB; jj++) {
+			const float4 pv = *reinterpret_cast<const float4*>(Pr + (size_t) jj * R + rb);
+			const float pa[4] = {pv.x, pv.y, pv.z, pv.w};
+			float va[CW];
+			if (CW == 4) {
+				const float4 vv = *reinterpret_cast<const float4*>(KV + jj * ldkv + 4 * nt);
+				va[0] = vv.x; va[1] = vv.y; va[CW - 2] = vv.z; va[CW - 1] = vv.w;
+			} else {
+				const float2 vv = *reinterpret_cast<const float2*>(KV + jj * ldkv + 2 * nt);
+				va[0] = vv.x; va[1] = vv.y;
+			}
+#pragma unroll
+			for (int i = 0; i < 4; i++)
+#pragma unroll
+				for (int u = 0; u < CW; u++) acc[i][u] = fmaf(pa[i], va[u], acc[i][u]);
+		}
+#pragma unroll
+		for (int i = 0; i < 4; i++) {
+			float* op = O + (size_t) (rb + i) * dvp + CW * nt;
+			const float al = alpha[rb + i];
+#pragma unroll
+			for (int u = 0; u < CW; u++) op[u] = fmaf(al, op[u], acc[i][u]);
 		}
 	}
 }
@@ -831,9 +868,10 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
 			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, a.ring, tid, nth);
 			__syncthreads();
-			if (kt == 4) swa_qk_tiles<4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
-			else if (kt == 2) swa_qk_tiles<2>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
-			else swa_qk_tiles<1>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			if (kt == 4) swa_qk_tiles<4, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			else if (kt == 2) swa_qk_tiles<2, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			else if ((Rg >> 2) * SWA_KB >= nth) swa_qk_tiles<1, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			else swa_qk_tiles<1, 2>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
 		}
 		__syncthreads();
 		// ---- mix the heads' scores (4 output heads per thread), mask ----
@@ -876,29 +914,8 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			__syncthreads(); // probabilities written; the last reader of KV is done
 			swa_load_tile(KV, ldkv, vc, G * dv, g * dv, dv, dvp, j0, nbk, a.ring, tid, nth);
 			__syncthreads();
-			const int NTv = dvp >> 2;
-			for (int tile = tid; tile < (Rg >> 2) * NTv; tile += nth) {
-				const int mt = tile / NTv, nt = tile % NTv, rb = g * Rg + 4 * mt;
-				float acc[4][4] = {};
-#pragma unroll 8
-				for (int jj = 0; jj < SWA_KB; jj++) {
-					const float4 pv = *reinterpret_cast<const float4*>(Pr + (size_t) jj * R + rb);
-					const float4 vv = *reinterpret_cast<const float4*>(KV + jj * ldkv + 4 * nt);
-					const float pa[4] = {pv.x, pv.y, pv.z, pv.w}, va[4] = {vv.x, vv.y, vv.z, vv.w};
-#pragma unroll
-					for (int i = 0; i < 4; i++)
-#pragma unroll
-						for (int u = 0; u < 4; u++) acc[i][u] = fmaf(pa[i], va[u], acc[i][u]);
-				}
-#pragma unroll
-				for (int i = 0; i < 4; i++) {
-					float4* op = reinterpret_cast<float4*>(O + (size_t) (rb + i) * dvp + 4 * nt);
-					const float al = alpha[rb + i];
-					float4 o = *op;
-					o.x = fmaf(al, o.x, acc[i][0]); o.y = fmaf(al, o.y, acc[i][1]); o.z = fmaf(al, o.z, acc[i][2]); o.w = fmaf(al, o.w, acc[i][3]);
-					*op = o;
-				}
-			}
+			if ((Rg >> 2) * (dvp >> 2) >= nth) swa_pv_tiles<4>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
+			else swa_pv_tiles<2>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
 		}
 	}
 	__syncthreads();
