@@ -1175,15 +1175,26 @@ inline size_t hgrn2_cols_smem_bytes(int dpl, int warps, int max_rows) {
 }
 
 // ---- y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb), layer scale, hyper-connection write -------------------------------------------------
+// The read of the sublayer that follows can ride along: with next.h set, the streams just written are combined with next.a, RMS-normed
+// with next.w and stored to next.h (what hc_norm_kernel would do in a launch of its own; the arithmetic is the same, in the same order).
+struct NextRead {
+	const float* a = nullptr; // (S) coefficients, NULL: ones
+	const float* w = nullptr; // (width) norm weight
+	int one_plus = 1;
+	float* h = nullptr;       // (T, width), NULL: nothing rides along
+};
 template <int SS>
 __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __restrict__ B, const float* __restrict__ wa, const float* __restrict__ wb,
-                                    float eps, int width, RowsEpi e) {
+                                    float eps, int width, RowsEpi e, NextRead next) {
 	extern __shared__ float sm[];
-	__shared__ float hm[MAX_STREAMS * MAX_STREAMS], ho[MAX_STREAMS];
-	float* red = sm;
+	__shared__ float hm[MAX_STREAMS * MAX_STREAMS], ho[MAX_STREAMS], an[MAX_STREAMS];
+	float* red = sm;      // 33
+	float* un = sm + 33;  // width, when next.h is set
 	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, S = e.S;
 	for (int x = tid; x < S * S; x += nth) hm[x] = e.hmix ? e.hmix[x] : (x / S == x % S ? 1.f : 0.f);
 	if (tid < S) ho[tid] = e.hout ? e.hout[tid] : 1.f;
+	if (tid < S) an[tid] = next.a ? next.a[tid] : 1.f;
+	float ssn = 0.f;
 	// four columns per thread at a time, loads first (see hc_norm_kernel)
 	float sa = 0.f, sb = 0.f;
 	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
@@ -1222,6 +1233,7 @@ __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __
 			if (c >= width) continue;
 			const float v = 0.5f * (x[k] * ra * wx[k] + y[k] * rb * wy[k]);
 			const float yv = e.scale ? sc[k] * v : v;
+			float u2 = 0.f;
 #pragma unroll
 			for (int q = 0; q < SS; q++)
 				if (q < S) {
@@ -1235,8 +1247,29 @@ __global__ void dual_norm_hc_kernel(const float* __restrict__ A, const float* __
 						for (int s2 = 0; s2 < SS; s2++)
 							if (s2 == q) acc = old[k][s2];
 					}
-					e.xs[(size_t) q * e.stream_stride + (size_t) t * width + c] = fmaf(ho[q], yv, acc);
+					const float nv = fmaf(ho[q], yv, acc);
+					e.xs[(size_t) q * e.stream_stride + (size_t) t * width + c] = nv;
+					u2 = next.a ? fmaf(an[q], nv, u2) : u2 + nv;
 				}
+			if (next.h) {
+				un[c] = u2;
+				ssn = fmaf(u2, u2, ssn);
+			}
+		}
+	}
+	if (!next.h) return;
+	const float rn = 1.f / sqrtf(block_sum(ssn, red) / (float) width + eps);
+	for (int c0 = 0; c0 < width; c0 += 4 * nth) {
+		float wv[4];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			wv[k] = c < width ? next.w[c] : 0.f;
+		}
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth + tid;
+			if (c < width) next.h[(size_t) t * width + c] = un[c] * rn * (next.one_plus ? 1.f + wv[k] : wv[k]); // un[c]: written by this thread
 		}
 	}
 }
@@ -1329,13 +1362,17 @@ static inline int launch_hc_norm(const float* xs, int S, size_t stream_stride, c
 	return launch_check("hc_norm");
 }
 
+// widths whose combined row fits the default 48 KB of dynamic shared memory can carry the next sublayer's read
+static inline bool dual_norm_can_carry(int width) { return (size_t) (width + 33) * 4 <= 48 * 1024; }
 static inline int launch_dual_norm_hc(const float* A, const float* B, const float* wa, const float* wb, float eps, int width, const RowsEpi& e, int rows,
-                                      cudaStream_t s) {
+                                      cudaStream_t s, const NextRead& next = NextRead()) {
 	const int nt = norm_threads(width);
-	if (e.S <= 1) dual_norm_hc_kernel<1><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
-	else if (e.S <= 2) dual_norm_hc_kernel<2><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
-	else if (e.S <= 4) dual_norm_hc_kernel<4><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
-	else dual_norm_hc_kernel<MAX_STREAMS><<<rows, nt, 33 * 4, s>>>(A, B, wa, wb, eps, width, e);
+	if (next.h && !dual_norm_can_carry(width)) return set_error(XALM_ERR_UNSUPPORTED, "dual_norm_hc: a row of %d does not fit shared memory", width);
+	const size_t smem = (size_t) (33 + (next.h ? width : 0)) * 4;
+	if (e.S <= 1) dual_norm_hc_kernel<1><<<rows, nt, smem, s>>>(A, B, wa, wb, eps, width, e, next);
+	else if (e.S <= 2) dual_norm_hc_kernel<2><<<rows, nt, smem, s>>>(A, B, wa, wb, eps, width, e, next);
+	else if (e.S <= 4) dual_norm_hc_kernel<4><<<rows, nt, smem, s>>>(A, B, wa, wb, eps, width, e, next);
+	else dual_norm_hc_kernel<MAX_STREAMS><<<rows, nt, smem, s>>>(A, B, wa, wb, eps, width, e, next);
 	return launch_check("dual_norm_hc");
 }
 

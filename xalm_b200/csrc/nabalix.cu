@@ -117,6 +117,7 @@ struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
 	float *xs = nullptr, *h = nullptr, *proj = nullptr, *att = nullptr, *ro = nullptr, *ol = nullptr, *orr = nullptr, *y = nullptr, *logits = nullptr;
 	float *part_o = nullptr, *part_ml = nullptr, *layer_sums = nullptr;
 	unsigned* tickets = nullptr; // per query tile: arrivals of the attention's key splits
+	int graph_launches[2] = {0, 0};    // kernels in the captured one-token step (without / with logits)
 	int part_cap = 0, keep_layers = 0; // part_cap: (token, key split) pairs the attention's partial buffers hold
 	int* d_tokens = nullptr;
 	SeqStep* d_step = nullptr;
@@ -408,12 +409,17 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 		if (overlap) XALM_CUDA_CHECK(cudaStreamWaitEvent(s, m->ev_join, 0));
 		est.out = m->orr;
 		XALM_TRY(rows_product(m, m->ro, Hr * dvr, L.w_ro, &L.t_ro, n, W, Hr * dvr, est, nl));
-		XALM_TRY(launch_dual_norm_hc(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0), n, s));
+		NextRead nx; // the feed-forward's read of the streams rides along with the mixer's write when the row fits
+		const bool carry = L.has_mlp && dual_norm_can_carry(W);
+		if (carry) { nx.a = L.hc_in[1]; nx.w = L.norm2; nx.one_plus = 1; nx.h = m->h; }
+		XALM_TRY(launch_dual_norm_hc(m->ol, m->orr, L.lout, L.rout, m->eps, W, hc_epi(m, L, 0), n, s, nx));
 		(*nl)++;
 		// ---- feed-forward ----
 		if (L.has_mlp) {
-			XALM_TRY(launch_hc_norm(m->xs, S, sstride, L.hc_in[1], L.norm2, 1, m->eps, W, m->h, nullptr, n, s));
-			(*nl)++;
+			if (!carry) {
+				XALM_TRY(launch_hc_norm(m->xs, S, sstride, L.hc_in[1], L.norm2, 1, m->eps, W, m->h, nullptr, n, s));
+				(*nl)++;
+			}
 			RowsEpi eg;
 			eg.kind = EPI_GLU; eg.out = m->y; eg.ldo = L.ff; eg.limit = L.limit;
 			XALM_TRY(rows_product(m, m->h, W, L.w_gu, &L.t_gu, n, 2 * L.ff, W, eg, nl));
@@ -454,6 +460,7 @@ int ensure_graph(Nb* m, int mode) {
 		return rc;
 	}
 	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+	m->graph_launches[mode] = nl;
 	e = cudaGraphInstantiate(&m->graph[mode], g, 0);
 	cudaGraphDestroy(g);
 	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
@@ -472,13 +479,7 @@ int run_pass(Nb* m, const int* tokens, int n, int want) {
 		const int mode = want ? 1 : 0;
 		XALM_TRY(ensure_graph(m, mode));
 		XALM_CUDA_CHECK(cudaGraphLaunch(m->graph[mode], m->stream));
-		nl = m->last_launches; // as counted at capture
-		int cnt = 0;
-		if (!m->last_launches) { // count once, without running: the same sequence the graph holds
-			cnt = 1 + (want ? 2 : 0);
-			for (const Layer& L : m->layers) cnt += 7 + (L.has_mlp ? 3 : 0) + (m->keep_layers ? 1 : 0);
-			nl = cnt;
-		}
+		nl = m->graph_launches[mode]; // as counted at capture
 	} else {
 		XALM_TRY(enqueue_pass(m, n, want, &nl));
 	}
