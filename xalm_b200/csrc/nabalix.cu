@@ -4,8 +4,9 @@
 // them as the mean of their RMS-normed outputs, follow with a clamped-GLU feed-forward, and carry the residual in several
 // hyper-connected streams with a layer scale on every sublayer.
 //
-// One step function serves prompts and generation (seq_step): n tokens of the running sequence, cut into passes of at most
-// "seq_chunk" positions.  Per pass and layer:
+// The step function, the graph of one-token steps, tensor upload and the entry points are the shared sequence engine's
+// (seq_family.cuh); this file holds what is Nabalix: its configuration, device layouts, cache and state, and the kernels of a pass.
+// Per pass and layer:
 //     hc_norm                      u = sum_s in[s] x_s -> RMS norm (1 + w)
 //     rows product [in-projection] one matrix [Lq | Lg | Rq | Rf | Rv | Lk | Lv]; the K/V columns go straight into the ring cache
 //     swa_attn (+ swa_merge)       left mixer, gate fused;   hgrn2: right mixer, activations + per-head norm fused
@@ -21,30 +22,13 @@
 // Precision: XALM_PRECISION_F32 computes everything in IEEE fp32 (weights are widened, the K/V ring holds fp32).  XALM_PRECISION_BF16
 // keeps weights and K/V ring in bf16 and routes batched matrix products whose shapes allow it through the tcgen05 GEMM of
 // prefill.cu (fp16 hi+lo operand pairs, fp32 accumulation); norms, scores, softmax, gates, the recurrence and the streams stay fp32.
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <math.h>
-#include <stdio.h>
-#include <stdlib.h>
-#include <string.h>
-
-#include <algorithm>
-#include <map>
-#include <string>
-#include <vector>
-
-#define XALM_SECONDARY_TU
-#include "common.cuh"
-#include "family.h"
-#include "formats.cuh"
-#include "host/json.h"
-#include "mix_ops.cuh"
-#include "prefill.h"
+#include "seq_family.cuh"
 
 namespace xalm {
 namespace {
 
 using namespace mix;
+using namespace seq;
 
 struct LeftCfg {
 	int H = 0, G = 0, d = 0, dv = 0, window = 0; // window 0: every earlier position is visible
@@ -54,15 +38,6 @@ struct RightCfg {
 	int H = 0, d = 0, dv = 0;
 };
 
-// a tensor as uploaded: fp32 on the host until finalize builds the device layouts
-struct HostTensor {
-	std::vector<int> shape;
-	bool required = true;
-	bool matrix = false;
-	bool got = false;
-	int type = 0;
-	std::vector<float> v;
-};
 
 struct Layer {
 	LeftCfg L;
@@ -88,72 +63,21 @@ struct Layer {
 	float* state = nullptr;
 };
 
-} // namespace
-} // namespace xalm
-
-using namespace xalm;
-using namespace xalm::mix;
-
-struct NabalixModel { // what a Nabalix handle points to (ModelHead first)
-	ModelHead head = {nullptr};
-	int device = 0, precision = XALM_PRECISION_BF16, max_tokens = 0;
-	int vocab = 0, width = 0, S = 1;
-	float eps = 1e-5f;
+struct NabalixModel : SeqModel {
+	int S = 1;
 	std::vector<Layer> layers;
-	std::map<std::string, HostTensor> tensors;
-	std::vector<std::string> order; // expected tensors in file order
-	bool w_bf16 = true;             // matrices live on the device as bf16 (else fp32)
-	bool finalized = false;
-	std::vector<void*> allocs;
-	void *embed = nullptr, *w_head = nullptr;
-	WMat m_head;
-	TcWeight t_head;
-	uint8_t *a_hi = nullptr, *a_lo = nullptr; // activation operand planes of the tensor-core path
-	float* tc_out = nullptr;                  // its plain fp32 product, when an epilogue follows
-	int tc_min_rows = 32;
-	float* final_norm = nullptr;
 	// activations of one pass
-	int chunk = 256;
-	float *xs = nullptr, *h = nullptr, *proj = nullptr, *att = nullptr, *ro = nullptr, *ol = nullptr, *orr = nullptr, *y = nullptr, *logits = nullptr;
-	float *part_o = nullptr, *part_ml = nullptr, *layer_sums = nullptr;
+	float *xs = nullptr, *h = nullptr, *proj = nullptr, *att = nullptr, *ro = nullptr, *ol = nullptr, *orr = nullptr, *y = nullptr;
+	float *part_o = nullptr, *part_ml = nullptr;
 	unsigned* tickets = nullptr; // per query tile: arrivals of the attention's key splits
-	int graph_launches[2] = {0, 0};    // kernels in the captured one-token step (without / with logits)
-	int part_cap = 0, keep_layers = 0; // part_cap: (token, key split) pairs the attention's partial buffers hold
-	int* d_tokens = nullptr;
-	SeqStep* d_step = nullptr;
-	float* h_logits = nullptr; // pinned, chunk x vocab
+	int part_cap = 0;            // (token, key split) pairs the attention's partial buffers hold
 	size_t proj_ld = 0;
-	cudaStream_t stream = nullptr, own_stream = nullptr;
-	cudaStream_t side = nullptr;                  // the recurrence of a layer runs here, beside the attention on `stream`
-	cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
-	cudaGraphExec_t graph[2] = {nullptr, nullptr};
-	int pos = 0; // tokens the running sequence holds
-	int last_launches = 0;
-	bool use_tc = false;
-	long long weight_bytes = 0, weight_bytes_tc = 0;
 };
-
-namespace xalm {
-namespace {
-
 typedef NabalixModel Nb;
 
 // ---- config.json ------------------------------------------------------------------------------------------------------------
-int geti(const xjson::Value& o, const char* k) {
-	const xjson::Value& v = o.at(k);
-	if (v.kind != xjson::Value::Number) throw std::invalid_argument(std::string("config: '") + k + "' is not a number");
-	return (int) v.num;
-}
-void expect(Nb* m, const std::string& name, std::vector<int> shape, bool matrix, bool required = true) {
-	HostTensor t;
-	t.shape = std::move(shape);
-	t.matrix = matrix;
-	t.required = required;
-	m->tensors.emplace(name, std::move(t));
-	m->order.push_back(name);
-}
-
-int parse_config(Nb* m, const char* json) {
+int parse_config(SeqModel* sm, const char* json) {
+	Nb* m = static_cast<Nb*>(sm);
 	try {
 		const xjson::Value c = xjson::Parser::parse(json, strlen(json));
 		m->vocab = geti(c, "vocab");
@@ -235,6 +159,7 @@ int parse_config(Nb* m, const char* json) {
 			}
 			m->layers.push_back(L);
 		}
+		m->n_layers = (int) m->layers.size();
 		expect(m, "final.norm", {W}, false);
 		expect(m, "head", {m->vocab, W}, true);
 	} catch (const std::exception& e) {
@@ -242,100 +167,6 @@ int parse_config(Nb* m, const char* json) {
 	}
 	return XALM_OK;
 }
-
-// ---- device memory ------------------------------------------------------------------------------------------------------------
-template <typename T>
-int dev_alloc(Nb* m, T** p, size_t count, bool zero = false) {
-	void* q = nullptr;
-	const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
-	cudaError_t e = cudaMalloc(&q, bytes);
-	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
-	m->allocs.push_back(q);
-	if (zero) XALM_CUDA_CHECK(cudaMemset(q, 0, bytes));
-	*p = reinterpret_cast<T*>(q);
-	return XALM_OK;
-}
-
-int upload_vec(Nb* m, const std::string& name, float** dst) {
-	*dst = nullptr;
-	const HostTensor& t = m->tensors.at(name);
-	if (!t.got) return XALM_OK;
-	XALM_TRY(dev_alloc(m, dst, t.v.size()));
-	XALM_CUDA_CHECK(cudaMemcpy(*dst, t.v.data(), t.v.size() * 4, cudaMemcpyHostToDevice));
-	m->weight_bytes += (long long) t.v.size() * 4;
-	return XALM_OK;
-}
-
-uint16_t f32_to_bf16_bits(float f) {
-	uint32_t u;
-	memcpy(&u, &f, 4);
-	if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t) ((u >> 16) | 0x40);
-	u += 0x7fffu + ((u >> 16) & 1u);
-	return (uint16_t) (u >> 16);
-}
-
-// rows of several host matrices, one after the other (interleave: rows of the two parts alternate), as one device matrix
-int upload_rows(Nb* m, const std::vector<const HostTensor*>& parts, int K, bool interleave, void** dst, WMat* wm) {
-	size_t rows = 0;
-	for (const HostTensor* t : parts) rows += t ? (size_t) t->shape[0] : 0;
-	const size_t esz = m->w_bf16 ? 2 : 4;
-	std::vector<uint8_t> buf(rows * (size_t) K * esz);
-	size_t r = 0;
-	auto put_row = [&](const float* src) {
-		if (m->w_bf16) {
-			uint16_t* o = reinterpret_cast<uint16_t*>(buf.data()) + r * (size_t) K;
-			for (int k = 0; k < K; k++) o[k] = f32_to_bf16_bits(src[k]);
-		} else memcpy(buf.data() + r * (size_t) K * 4, src, (size_t) K * 4);
-		r++;
-	};
-	if (interleave) {
-		for (int i = 0; i < parts[0]->shape[0]; i++)
-			for (const HostTensor* t : parts) put_row(t->v.data() + (size_t) i * K);
-	} else {
-		for (const HostTensor* t : parts)
-			if (t)
-				for (int i = 0; i < t->shape[0]; i++) put_row(t->v.data() + (size_t) i * K);
-	}
-	uint8_t* d = nullptr;
-	XALM_TRY(dev_alloc(m, &d, buf.size() + 64));
-	XALM_CUDA_CHECK(cudaMemcpy(d, buf.data(), buf.size(), cudaMemcpyHostToDevice));
-	*dst = d;
-	m->weight_bytes += (long long) buf.size();
-	if (wm) {
-		*wm = WMat();
-		wm->type = m->w_bf16 ? XALM_BF16 : XALM_F32;
-		wm->rows = (int) rows;
-		wm->n = K;
-		wm->p0 = d;
-		wm->s0 = (size_t) K * esz;
-	}
-	return XALM_OK;
-}
-
-// ---- row products -------------------------------------------------------------------------------------------------------------
-// Passes of few tokens and the fp32 mode: the fp32 FMA kernels of mix_ops.cuh with the epilogue fused.  Passes of tc_min_rows tokens
-// or more in the 16-bit mode: the tcgen05 GEMM of prefill.cu on the weight's resident fp16 tiles (activations packed to fp16, one
-// plane, or hi + lo with "seq_tc" = 2), fp32 accumulation, then the same epilogue as an elementwise kernel.
-int rows_product(Nb* m, const float* A, int lda, const void* W, const TcWeight* tw, int T, int N, int K, const RowsEpi& e, int* nl) {
-	if (m->use_tc && tw && tw->hi && T >= m->tc_min_rows && lda == K) {
-		if (e.kind == EPI_STORE && e.ldo % 4 == 0) {
-			*nl += 2;
-			return tc_gemm(*tw, A, T, e.out, e.ldo, m->a_hi, m->a_lo, m->stream);
-		}
-		*nl += 3;
-		XALM_TRY(tc_gemm(*tw, A, T, m->tc_out, N, m->a_hi, m->a_lo, m->stream));
-		return launch_rows_epilogue(m->tc_out, N, T, N, e, m->stream);
-	}
-	(*nl)++;
-	return launch_rows(A, lda, W, m->w_bf16, T, N, K, e, m->stream);
-}
-
-#define NB_LAUNCH_CHECK(what)                                                                                       \
-	do {                                                                                                            \
-		(*nl)++;                                                                                                    \
-		cudaError_t e_ = cudaGetLastError();                                                                        \
-		if (e_ != cudaSuccess) return set_error(XALM_ERR_CUDA, what " launch failed: %s", cudaGetErrorString(e_));   \
-	} while (0)
 
 // hyper-connection write of sublayer q of layer L as an epilogue
 RowsEpi hc_epi(Nb* m, const Layer& L, int q) {
@@ -351,14 +182,15 @@ RowsEpi hc_epi(Nb* m, const Layer& L, int q) {
 }
 
 // the kernels of one pass: n tokens (ids in d_tokens, position in d_step).  want: 0 no logits, 1 the last row's, 2 every row's.
-int enqueue_pass(Nb* m, int n, int want, int* nl) {
+int enqueue_pass(SeqModel* sm, int n, int want, int* nl) {
+	Nb* m = static_cast<Nb*>(sm);
 	cudaStream_t s = m->stream;
 	const int W = m->width, S = m->S;
 	const size_t sstride = (size_t) m->chunk * W;
 	const int rt = norm_threads(W);
 	if (m->w_bf16) embed_streams_kernel<__nv_bfloat16><<<n, rt, 0, s>>>((const __nv_bfloat16*) m->embed, m->d_tokens, W, S, sstride, m->xs);
 	else embed_streams_kernel<float><<<n, rt, 0, s>>>((const float*) m->embed, m->d_tokens, W, S, sstride, m->xs);
-	NB_LAUNCH_CHECK("embed");
+	XALM_SEQ_LAUNCH_CHECK("embed");
 	for (size_t li = 0; li < m->layers.size(); li++) {
 		const Layer& L = m->layers[li];
 		const int H = L.L.H, G = L.L.G, d = L.L.d, dv = L.L.dv, Hr = L.R.H, dr = L.R.d, dvr = L.R.dv;
@@ -441,184 +273,11 @@ int enqueue_pass(Nb* m, int n, int want, int* nl) {
 	return XALM_OK;
 }
 
-int check_ready(Nb* m) {
-	if (!m) return set_error(XALM_ERR_INVALID, "model is NULL");
-	if (!m->finalized) return set_error(XALM_ERR_STATE, "the model is not finalized");
-	XALM_CUDA_CHECK(cudaSetDevice(m->device));
-	return XALM_OK;
-}
-
-int ensure_graph(Nb* m, int mode) {
-	if (m->graph[mode]) return XALM_OK;
-	cudaGraph_t g = nullptr;
-	XALM_CUDA_CHECK(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-	int nl = 0;
-	const int rc = enqueue_pass(m, 1, mode ? 1 : 0, &nl);
-	cudaError_t e = cudaStreamEndCapture(m->stream, &g);
-	if (rc != XALM_OK) {
-		if (g) cudaGraphDestroy(g);
-		return rc;
-	}
-	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
-	m->graph_launches[mode] = nl;
-	e = cudaGraphInstantiate(&m->graph[mode], g, 0);
-	cudaGraphDestroy(g);
-	if (e != cudaSuccess) return set_error(XALM_ERR_CUDA, "cudaGraphInstantiate failed: %s", cudaGetErrorString(e));
-	return XALM_OK;
-}
-
-// one pass of n <= chunk tokens at the sequence's position; the logits (want) stay on the device
-int run_pass(Nb* m, const int* tokens, int n, int want) {
-	for (int i = 0; i < n; i++)
-		if (tokens[i] < 0 || tokens[i] >= m->vocab) return set_error(XALM_ERR_INVALID, "token %d out of range", tokens[i]);
-	const SeqStep st = {m->pos, n};
-	XALM_CUDA_CHECK(cudaMemcpyAsync(m->d_tokens, tokens, (size_t) n * 4, cudaMemcpyHostToDevice, m->stream));
-	XALM_CUDA_CHECK(cudaMemcpyAsync(m->d_step, &st, sizeof st, cudaMemcpyHostToDevice, m->stream));
-	int nl = 0;
-	if (n == 1 && tune("seq_graph")) {
-		const int mode = want ? 1 : 0;
-		XALM_TRY(ensure_graph(m, mode));
-		XALM_CUDA_CHECK(cudaGraphLaunch(m->graph[mode], m->stream));
-		nl = m->graph_launches[mode]; // as counted at capture
-	} else {
-		XALM_TRY(enqueue_pass(m, n, want, &nl));
-	}
-	m->last_launches = nl;
-	m->pos += n;
-	return XALM_OK;
-}
-
-// the step function: n tokens of the running sequence from position pos0 (= what the sequence holds)
-int seq_step(Nb* m, const int* tokens, int n, int pos0, int want, float* logits_host, const int* targets, float* probs_host) {
-	XALM_TRY(check_ready(m));
-	if (!tokens || n <= 0) return set_error(XALM_ERR_INVALID, "step: no tokens");
-	if (want < 0 || want > 2) return set_error(XALM_ERR_INVALID, "step: want_logits = %d", want);
-	if (targets && want != 2) return set_error(XALM_ERR_INVALID, "step: target probabilities need the logits of every position");
-	if (pos0 != m->pos)
-		return set_error(XALM_ERR_STATE, "step: position %d, but the sequence holds %d tokens (release it to start another)", pos0, m->pos);
-	if ((long long) pos0 + n > m->max_tokens) return set_error(XALM_ERR_INVALID, "step: positions [%d, %d) exceed max_tokens %d", pos0, pos0 + n, m->max_tokens);
-	const int V = m->vocab;
-	for (int at = 0; at < n; at += m->chunk) {
-		const int nc = std::min(m->chunk, n - at);
-		const bool last = at + nc == n;
-		const int w = want == 2 ? 2 : (want == 1 && last ? 1 : 0);
-		XALM_TRY(run_pass(m, tokens + at, nc, w));
-		if (w) {
-			const int rows = w == 2 ? nc : 1;
-			XALM_CUDA_CHECK(cudaMemcpyAsync(m->h_logits, m->logits, (size_t) rows * V * 4, cudaMemcpyDeviceToHost, m->stream));
-			XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-			if (logits_host) memcpy(logits_host + (w == 2 ? (size_t) at * V : 0), m->h_logits, (size_t) rows * V * 4);
-			if (targets && probs_host)
-				for (int i = 0; i < rows; i++) { // Sampler::sample_prob (sampler.cpp:18-33)
-					const float* lg = m->h_logits + (size_t) i * V;
-					if (targets[at + i] < 0 || targets[at + i] >= V) return set_error(XALM_ERR_INVALID, "step: target %d out of range", targets[at + i]);
-					float top = lg[0];
-					for (int k = 1; k < V; k++) top = std::max(top, lg[k]);
-					float den = 0.f;
-					for (int k = 0; k < V; k++) den += expf(lg[k] - top);
-					probs_host[at + i] = expf(lg[targets[at + i]] - top) / den;
-				}
-		}
-	}
-	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-	return XALM_OK;
-}
-
-// ---- family table ---------------------------------------------------------------------------------------------------------------
-void nb_destroy(Nb* m) {
-	if (!m) return;
-	cudaSetDevice(m->device);
-	if (m->stream) cudaStreamSynchronize(m->stream);
-	for (int i = 0; i < 2; i++)
-		if (m->graph[i]) cudaGraphExecDestroy(m->graph[i]);
-	for (void* p : m->allocs) cudaFree(p);
-	for (Layer& L : m->layers)
-		for (TcWeight* t : {&L.t_in, &L.t_lo, &L.t_ro, &L.t_gu, &L.t_down}) tc_weight_free(t);
-	tc_weight_free(&m->t_head);
-	if (m->h_logits) cudaFreeHost(m->h_logits);
-	if (m->own_stream) cudaStreamDestroy(m->own_stream);
-	if (m->side) cudaStreamDestroy(m->side);
-	if (m->ev_fork) cudaEventDestroy(m->ev_fork);
-	if (m->ev_join) cudaEventDestroy(m->ev_join);
-	delete m;
-}
-
-extern const ModelFamily nabalix_family;
-
-int nb_create(const char* json, int device, int max_tokens, int precision, Nb** out) {
-	if (max_tokens <= 0) return set_error(XALM_ERR_INVALID, "max_tokens must be positive");
-	Nb* m = new Nb();
-	m->head.family = &nabalix_family;
-	m->device = device;
-	m->precision = precision;
-	m->max_tokens = max_tokens;
-	const int rc = parse_config(m, json); // before the device is touched: a bad config is reported as such on any machine
-	if (rc != XALM_OK) { delete m; return rc; }
-	int ndev = 0;
-	cudaError_t e = cudaGetDeviceCount(&ndev);
-	if (e != cudaSuccess) { delete m; return set_error(XALM_ERR_CUDA, "cudaGetDeviceCount failed: %s", cudaGetErrorString(e)); }
-	if (device < 0 || device >= ndev) { delete m; return set_error(XALM_ERR_CUDA, "device %d not available (%d devices)", device, ndev); }
-	e = cudaSetDevice(device);
-	if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->own_stream, cudaStreamNonBlocking);
-	if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking);
-	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming);
-	if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming);
-	if (e != cudaSuccess) { delete m; return set_error(XALM_ERR_CUDA, "cudaStreamCreate failed: %s", cudaGetErrorString(e)); }
-	m->stream = m->own_stream;
-	*out = m;
-	return XALM_OK;
-}
-
-int nb_upload(Nb* m, const char* name, int type_id, const int* shape, int rank, const void* data, size_t nbytes) {
-	if (!m || !name || !shape || !data) return set_error(XALM_ERR_INVALID, "NULL argument");
-	if (m->finalized) return set_error(XALM_ERR_STATE, "upload after finalize");
-	auto it = m->tensors.find(name);
-	if (it == m->tensors.end()) return set_error(XALM_ERR_INVALID, "unknown tensor name '%s'", name);
-	HostTensor& t = it->second;
-	bool same = (size_t) rank == t.shape.size();
-	size_t count = 1;
-	for (int i = 0; same && i < rank; i++) same = shape[i] == t.shape[(size_t) i];
-	for (int dsz : t.shape) count *= (size_t) dsz;
-	if (!same) return set_error(XALM_ERR_INVALID, "shape mismatch for %s", name);
-	const size_t esz = type_id == XALM_F32 ? 4 : (type_id == XALM_F16 || type_id == XALM_BF16) ? 2 : 0;
-	if (!esz) return set_error(XALM_ERR_UNSUPPORTED, "tensor %s: type %d (F32, F16 or BF16)", name, type_id);
-	if (nbytes != count * esz) return set_error(XALM_ERR_INVALID, "size mismatch for %s", name);
-	t.v.resize(count);
-	if (type_id == XALM_F32) memcpy(t.v.data(), data, nbytes);
-	else if (type_id == XALM_BF16) {
-		const uint16_t* b = static_cast<const uint16_t*>(data);
-		for (size_t i = 0; i < count; i++) {
-			const uint32_t u = (uint32_t) b[i] << 16;
-			memcpy(&t.v[i], &u, 4);
-		}
-	} else {
-		const __half* hsrc = static_cast<const __half*>(data);
-		for (size_t i = 0; i < count; i++) t.v[i] = __half2float(hsrc[i]);
-	}
-	t.type = type_id;
-	t.got = true;
-	return XALM_OK;
-}
-
-int nb_finalize(Nb* m) {
-	if (!m) return set_error(XALM_ERR_INVALID, "model is NULL");
-	if (m->finalized) return XALM_OK;
-	XALM_CUDA_CHECK(cudaSetDevice(m->device));
-	m->w_bf16 = m->precision != XALM_PRECISION_F32;
-	for (const auto& [name, t] : m->tensors) {
-		if (t.required && !t.got) return set_error(XALM_ERR_STATE, "tensor %s was not uploaded", name.c_str());
-		if (t.matrix && t.got && t.type != XALM_BF16) m->w_bf16 = false; // wider checkpoints keep their precision
-	}
+// ---- device layouts, cache, state, pass buffers ---------------------------------------------------------------------------------
+int finalize(SeqModel* sm) {
+	Nb* m = static_cast<Nb*>(sm);
 	const int W = m->width, S = m->S;
-	m->chunk = std::max(8, std::min(tune("seq_chunk"), 4096));
-	m->keep_layers = getenv("XALM_SEQ_KEEP_LAYERS") ? atoi(getenv("XALM_SEQ_KEEP_LAYERS")) : 0;
-	auto T = [&](const std::string& n) -> const HostTensor* {
-		const HostTensor& t = m->tensors.at(n);
-		return t.got ? &t : nullptr;
-	};
-	XALM_TRY(upload_rows(m, {T("embed")}, W, false, &m->embed, nullptr));
-	XALM_TRY(upload_rows(m, {T("head")}, W, false, &m->w_head, &m->m_head));
-	XALM_TRY(upload_vec(m, "final.norm", &m->final_norm));
+	auto T = [&](const std::string& n) { return tensor_or_null(m, n); };
 	size_t max_proj = 0, max_att = 0, max_ro = 0, max_ff = 1, max_hdv = 0, max_h = 1;
 	int max_ring = 1;
 	for (size_t li = 0; li < m->layers.size(); li++) {
@@ -685,35 +344,14 @@ int nb_finalize(Nb* m) {
 		XALM_TRY(hgrn2_prepare(dr, dvr));
 	}
 	XALM_TRY(hc_norm_prepare(W));
-	// tensor-core operands: every matrix whose shape the GEMM takes keeps its fp16 tiles beside the bf16 rows the one-token steps stream
-	m->use_tc = m->w_bf16 && tune("seq_tc") > 0;
-	m->tc_min_rows = std::max(1, tune("seq_tc_min"));
-	size_t a_bytes = 0, tc_cols = 4;
-	if (m->use_tc) {
-		auto build = [&](const WMat& wm, TcWeight* t) -> int {
-			if (!tc_shape_ok(wm.rows, wm.n, wm.rows)) return XALM_OK; // this one stays on the fp32 kernels
-			XALM_TRY(tc_weight_build(wm, 1, t, m->stream));
-			a_bytes = std::max(a_bytes, tc_a_plane_bytes(m->chunk, wm.n));
-			tc_cols = std::max(tc_cols, (size_t) wm.rows);
-			m->weight_bytes_tc += (long long) t->NT * t->KT * 256 * 64 * 2;
-			return XALM_OK;
-		};
-		for (Layer& L : m->layers) {
-			XALM_TRY(build(L.m_in, &L.t_in));
-			XALM_TRY(build(L.m_lo, &L.t_lo));
-			XALM_TRY(build(L.m_ro, &L.t_ro));
-			if (L.has_mlp) {
-				XALM_TRY(build(L.m_gu, &L.t_gu));
-				XALM_TRY(build(L.m_down, &L.t_down));
-			}
+	for (Layer& L : m->layers) {
+		XALM_TRY(tc_register(m, L.m_in, &L.t_in));
+		XALM_TRY(tc_register(m, L.m_lo, &L.t_lo));
+		XALM_TRY(tc_register(m, L.m_ro, &L.t_ro));
+		if (L.has_mlp) {
+			XALM_TRY(tc_register(m, L.m_gu, &L.t_gu));
+			XALM_TRY(tc_register(m, L.m_down, &L.t_down));
 		}
-		XALM_TRY(build(m->m_head, &m->t_head));
-		if (a_bytes) {
-			XALM_TRY(dev_alloc(m, &m->a_hi, a_bytes, true));
-			if (tune("seq_tc") >= 2) XALM_TRY(dev_alloc(m, &m->a_lo, a_bytes, true));
-			XALM_TRY(dev_alloc(m, &m->tc_out, (size_t) m->chunk * tc_cols));
-		} else m->use_tc = false;
-		XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
 	}
 	m->proj_ld = (max_proj + 3) / 4 * 4;
 	const size_t C = (size_t) m->chunk;
@@ -730,149 +368,49 @@ int nb_finalize(Nb* m) {
 	XALM_TRY(dev_alloc(m, &m->part_o, (size_t) m->part_cap * max_hdv));
 	XALM_TRY(dev_alloc(m, &m->part_ml, (size_t) m->part_cap * 2 * max_h));
 	XALM_TRY(dev_alloc(m, &m->tickets, C, true));
-	if (m->keep_layers) XALM_TRY(dev_alloc(m, &m->layer_sums, m->layers.size() * C * W, true));
-	XALM_TRY(dev_alloc(m, &m->d_tokens, C));
-	XALM_TRY(dev_alloc(m, &m->d_step, 1));
-	XALM_CUDA_CHECK(cudaMallocHost(&m->h_logits, C * m->vocab * 4));
-	for (auto& [name, t] : m->tensors) std::vector<float>().swap(t.v); // the device owns the weights from here on
-	m->finalized = true;
+	(void) max_ring;
 	return XALM_OK;
 }
 
-int nb_release(Nb* m) {
-	XALM_TRY(check_ready(m));
-	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
+int release(SeqModel* sm) {
+	Nb* m = static_cast<Nb*>(sm);
 	for (Layer& L : m->layers) XALM_CUDA_CHECK(cudaMemsetAsync(L.state, 0, (size_t) L.R.H * L.R.d * L.R.dv * 4, m->stream));
-	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-	m->pos = 0;
 	return XALM_OK;
 }
 
-int nb_forward(Nb* m, int token, int pos, int mode, float* logits_host) {
-	return seq_step(m, &token, 1, pos, mode == XALM_OUTPUT_LOGITS ? 1 : 0, logits_host, nullptr, nullptr);
-}
-int nb_forward_async(Nb* m, int token, int pos, int mode) {
-	XALM_TRY(check_ready(m));
-	if (pos != m->pos) return set_error(XALM_ERR_STATE, "step: position %d, but the sequence holds %d tokens", pos, m->pos);
-	if (pos + 1 > m->max_tokens) return set_error(XALM_ERR_INVALID, "step: position %d exceeds max_tokens %d", pos, m->max_tokens);
-	return run_pass(m, &token, 1, mode == XALM_OUTPUT_LOGITS ? 1 : 0);
-}
-int nb_forward_argmax(Nb* m, int token, int pos, int* next) {
-	if (!next) return set_error(XALM_ERR_INVALID, "next_token is NULL");
-	XALM_TRY(seq_step(m, &token, 1, pos, 1, nullptr, nullptr, nullptr));
-	int best = 0;
-	for (int i = 1; i < m->vocab; i++)
-		if (m->h_logits[i] > m->h_logits[best]) best = i;
-	*next = best;
-	return XALM_OK;
-}
-int nb_sync(Nb* m) {
-	XALM_TRY(check_ready(m));
-	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-	return XALM_OK;
-}
-int nb_prefill(Nb* m, const int* tokens, int n, int pos0, int want, float* logits_host, const int* targets, float* probs_host) {
-	return seq_step(m, tokens, n, pos0, want, logits_host, targets, probs_host);
-}
-int nb_prefill_async(Nb* m, const int* tokens, int n, int pos0, int want) {
-	XALM_TRY(check_ready(m));
-	if (!tokens || n <= 0) return set_error(XALM_ERR_INVALID, "step: no tokens");
-	if (pos0 != m->pos) return set_error(XALM_ERR_STATE, "step: position %d, but the sequence holds %d tokens", pos0, m->pos);
-	if ((long long) pos0 + n > m->max_tokens) return set_error(XALM_ERR_INVALID, "step: positions exceed max_tokens %d", m->max_tokens);
-	int total = 0;
-	for (int at = 0; at < n; at += m->chunk) {
-		const int nc = std::min(m->chunk, n - at);
-		XALM_TRY(run_pass(m, tokens + at, nc, want == 2 ? 2 : (want == 1 && at + nc == n ? 1 : 0)));
-		total += m->last_launches;
-	}
-	m->last_launches = total;
-	return XALM_OK;
-}
-float* nb_logits_host(Nb* m) { return m ? m->h_logits : nullptr; }
-int nb_set_stream(Nb* m, void* s) {
-	if (!m) return set_error(XALM_ERR_INVALID, "model is NULL");
-	m->stream = s ? (cudaStream_t) s : m->own_stream;
-	return XALM_OK;
-}
-int nb_active_bytes(Nb* m, long long pos, long long* bytes) {
-	if (!m || !bytes) return set_error(XALM_ERR_INVALID, "NULL argument");
-	// what a one-token step at `pos` reads: every weight once (one embedding row), the visible K/V rows, the recurrent state twice
-	long long b = m->weight_bytes - (long long) (m->vocab - 1) * m->width * (m->w_bf16 ? 2 : 4);
+// beyond the matrices: the visible K/V rows, the recurrent state twice
+long long active_bytes(SeqModel* sm, long long pos) {
+	Nb* m = static_cast<Nb*>(sm);
+	long long b = 0;
 	const long long kelem = m->precision == XALM_PRECISION_F32 ? 4 : 2;
 	for (const Layer& L : m->layers) {
 		const long long seen = L.L.window > 0 ? std::min<long long>(pos + 1, L.L.window) : pos + 1;
 		b += seen * L.L.G * (L.L.d + L.L.dv) * kelem + 2ll * L.R.H * L.R.d * L.R.dv * 4;
 	}
-	*bytes = b;
-	return XALM_OK;
-}
-int nb_last_launch_count(Nb* m, int* n) {
-	if (!m || !n) return set_error(XALM_ERR_INVALID, "NULL argument");
-	*n = m->last_launches;
-	return XALM_OK;
-}
-// which: XALM_S_LOGITS = logits of the last pass (rows x vocab); 100 + l = the residual stream (sum of the streams) after layer l for the
-// rows of the last pass (kept only when XALM_SEQ_KEEP_LAYERS=1 was set at finalize); 1000 + l = recurrent state of layer l
-int nb_read_state(Nb* m, int which, float* dst, size_t n) {
-	XALM_TRY(check_ready(m));
-	if (!dst) return set_error(XALM_ERR_INVALID, "dst is NULL");
-	XALM_CUDA_CHECK(cudaStreamSynchronize(m->stream));
-	const float* src = nullptr;
-	size_t cap = 0;
-	if (which == XALM_S_LOGITS) { src = m->logits; cap = (size_t) m->chunk * m->vocab; }
-	else if (which >= 100 && which < 100 + (int) m->layers.size() && m->layer_sums) {
-		src = m->layer_sums + (size_t) (which - 100) * m->chunk * m->width;
-		cap = (size_t) m->chunk * m->width;
-	} else if (which >= 1000 && which < 1000 + (int) m->layers.size()) {
-		const Layer& L = m->layers[(size_t) (which - 1000)];
-		src = L.state;
-		cap = (size_t) L.R.H * L.R.d * L.R.dv;
-	} else return set_error(XALM_ERR_INVALID, "read_state: buffer %d", which);
-	if (n > cap) return set_error(XALM_ERR_INVALID, "read_state: %zu elements requested, buffer holds %zu", n, cap);
-	XALM_CUDA_CHECK(cudaMemcpy(dst, src, n * 4, cudaMemcpyDeviceToHost));
-	return XALM_OK;
-}
-int nb_expected_tensor(Nb* m, int index, char* name, size_t cap, int* shape4, int* rank) {
-	if (!m || !name || !shape4 || !rank) return set_error(XALM_ERR_INVALID, "NULL argument");
-	if (index < 0 || index >= (int) m->order.size()) return set_error(XALM_ERR_INVALID, "no tensor %d", index);
-	const std::string& nm = m->order[(size_t) index];
-	const HostTensor& t = m->tensors.at(nm);
-	snprintf(name, cap, "%s", nm.c_str());
-	*rank = (int) t.shape.size();
-	for (size_t i = 0; i < t.shape.size() && i < 4; i++) shape4[i] = t.shape[i];
-	return XALM_OK;
-}
-int nb_info(Nb* m, const char* key, long long* value) {
-	if (!m || !key || !value) return set_error(XALM_ERR_INVALID, "NULL argument");
-	const std::string k = key;
-	if (k == "vocab_size") *value = m->vocab;
-	else if (k == "dim") *value = m->width;
-	else if (k == "n_layers") *value = (long long) m->layers.size();
-	else if (k == "max_tokens") *value = m->max_tokens;
-	else if (k == "position") *value = m->pos;
-	else if (k == "chunk") *value = m->chunk;
-	else return set_error(XALM_ERR_INVALID, "unknown property '%s'", key);
-	return XALM_OK;
+	return b;
 }
 
-// the family table speaks in opaque handles
-template <auto F>
-struct Thunk;
-template <typename... A, int (*F)(Nb*, A...)>
-struct Thunk<F> {
-	static int call(xalm_cuda_model* h, A... a) { return F(reinterpret_cast<Nb*>(h), a...); }
-};
-int create_thunk(const char* json, int device, int max_tokens, int precision, xalm_cuda_model** out) {
-	return nb_create(json, device, max_tokens, precision, reinterpret_cast<Nb**>(out));
+bool state_buffer(SeqModel* sm, int layer, const float** src, size_t* count) {
+	Nb* m = static_cast<Nb*>(sm);
+	const Layer& L = m->layers[(size_t) layer];
+	*src = L.state;
+	*count = (size_t) L.R.H * L.R.d * L.R.dv;
+	return true;
 }
-void destroy_thunk(xalm_cuda_model* h) { nb_destroy(reinterpret_cast<Nb*>(h)); }
-float* logits_thunk(xalm_cuda_model* h) { return nb_logits_host(reinterpret_cast<Nb*>(h)); }
 
-const ModelFamily nabalix_family = {
-    "Nabalix", create_thunk, Thunk<nb_upload>::call, nullptr, nullptr, Thunk<nb_finalize>::call, destroy_thunk, nullptr, nullptr, nullptr,
-    Thunk<nb_set_stream>::call, Thunk<nb_forward>::call, Thunk<nb_forward_argmax>::call, Thunk<nb_forward_async>::call, Thunk<nb_sync>::call,
-    Thunk<nb_prefill>::call, Thunk<nb_prefill_async>::call, logits_thunk, Thunk<nb_active_bytes>::call, Thunk<nb_last_launch_count>::call,
-    Thunk<nb_read_state>::call, nullptr, nullptr, Thunk<nb_release>::call, Thunk<nb_expected_tensor>::call, Thunk<nb_info>::call, nullptr};
+void destroy(SeqModel* sm) {
+	Nb* m = static_cast<Nb*>(sm);
+	for (Layer& L : m->layers)
+		for (TcWeight* t : {&L.t_in, &L.t_lo, &L.t_ro, &L.t_gu, &L.t_down}) tc_weight_free(t);
+	delete m;
+}
+
+const SeqHooks nabalix_hooks = {parse_config, finalize, enqueue_pass, release, active_bytes, state_buffer, destroy};
+extern const ModelFamily nabalix_family;
+int create(const char* json, int device, int max_tokens, int precision, xalm_cuda_model** out) {
+	return seq_create<Nb>(&nabalix_family, &nabalix_hooks, json, device, max_tokens, precision, out);
+}
+const ModelFamily nabalix_family = seq_family_table("Nabalix", create);
 const FamilyRegistrar nabalix_registrar(&nabalix_family);
 
 } // namespace
