@@ -151,6 +151,34 @@ int xalm_cuda_hyper_norm(float* h, const float* xs, int S, int T, int W, const f
 int xalm_cuda_dual_norm_hyper(float* xs, const float* a, const float* b, const float* wa, const float* wb, float eps, int S, int T, int W,
                               const float* mix, const float* out_coef, const float* scale);
 int xalm_cuda_glu_rows(float* out, const float* x, const float* w_gate, const float* w_up, int T, int ff, int K, float limit, float alpha, int w_bf16);
+/* swa_attention_kept: the same window, but every position j < keep_first stays visible to all later queries (at its true position); the
+ *   cache holds those in slots of their own and the rest in a ring of `ring` slots.  No soft cap, bias, mixing or gate.
+ * group_norm_residual: x_out = x_in + gnorm(sum_k part_w[t, k] y[t * parts + k]) * w, gnorm = RMS norm over each of `groups` equal parts of
+ *   the row (x_in NULL: no residual; part_w NULL: parts == 1).  With dwa (n_hist + 1 coefficients) and hist (n_hist, T, W):
+ *   avg_out = sum_j dwa[j] hist[j] + dwa[n_hist] x_out.
+ * qkv_post: rows of [q (H d) | k (G d) | v (G dv)] for positions pos0..: bias, rotation of the first 2 rot_half dimensions of every q / k head
+ *   (dimension i with i + rot_half, angle = position * freq[i]), then weightless RMS norms of q, k heads (norm_qk) and v heads (norm_v).
+ *   q_out (T, H d); k_out / v_out: the whole cache (keep_first + ring slots), position p in slot p (p < keep_first) or
+ *   keep_first + (p - keep_first) % ring.
+ * delta_rule: T tokens of the gated delta rule.  q, k (T, G d) and v (T, H dv) are the projections BEFORE the causal convolutions
+ *   (weights (channels, taps), last column = the current token) and silu; q and k heads are then scaled to unit length
+ *   (x / sqrt(sum x^2 + unit_eps); q times q_scale); beta = sigmoid(b), g = exp(-exp(A_log) softplus(a + dt_bias)); per head
+ *   S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q; out = o / rms(o) * norm_w * silu(gate).  state (H, d, dv) and conv_state
+ *   (taps - 1, 2 G d + H dv: the last inputs of the q | k | v channels, oldest first) are read and written.
+ * moe_ffn: router scores s = sigmoid(h W_router^T); with n_groups > 1 the experts form equal groups of neighbours, a group scores the sum of its
+ *   two largest s and only the keep_groups best groups can be chosen from; idx / wgt (T, top) = the chosen experts and their scores;
+ *   out_pairs (T * top, K) = W_down[e] (act(W_gate[e] h) * (W_up[e] h)) for every chosen (token, expert); act: 1 silu, 2 tanh-gelu. */
+int xalm_cuda_swa_attention_kept(float* out, const float* q, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv, int window,
+                                 int keep_first, float scale, int ring, int n_splits, int cache_bf16);
+int xalm_cuda_group_norm_residual(float* x_out, float* avg_out, const float* y, int parts, const float* part_w, const float* w, int groups, float eps,
+                                  const float* x_in, const float* hist, int n_hist, const float* dwa, int T, int W);
+int xalm_cuda_qkv_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, int dv, const float* bq,
+                       const float* bk, const float* bv, const float* freq, int rot_half, int norm_qk, int norm_v, float eps, int keep_first, int ring);
+int xalm_cuda_delta_rule(float* out, float* state, float* conv_state, const float* q, const float* k, const float* v, const float* gate, const float* b,
+                         const float* a_in, int T, int H, int G, int d, int dv, int taps, const float* wq, const float* wk, const float* wv,
+                         const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps, float q_scale);
+int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
+                      const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16);
 
 /* Tensor parallel plumbing (no reference analogue; north star).  Rank 0 makes an id, the host side ships it to
  * the other ranks (torch.distributed / MPI / a file), every rank calls comm_init before finalize. */

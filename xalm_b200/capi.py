@@ -91,6 +91,11 @@ SYMBOLS = {
     "xalm_cuda_hyper_norm": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _i, C.c_float]),
     "xalm_cuda_dual_norm_hyper": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_float, _i, _i, _i, _vp, _vp, _vp]),
     "xalm_cuda_glu_rows": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, C.c_float, _i]),
+    "xalm_cuda_swa_attention_kept": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, C.c_float, _i, _i, _i]),
+    "xalm_cuda_group_norm_residual": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, C.c_float, _vp, _vp, _i, _vp, _i, _i]),
+    "xalm_cuda_qkv_post": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, C.c_float, _i, _i]),
+    "xalm_cuda_delta_rule": (_i, [_vp] * 9 + [_i] * 6 + [_vp] * 6 + [C.c_float] * 3),
+    "xalm_cuda_moe_ffn": (_i, [_vp] * 8 + [_i] * 9),
 }
 PRECISION_BF16, PRECISION_F32 = 0, 1            # enum xalm_precision
 
@@ -298,3 +303,64 @@ def glu_rows(x, w_gate, w_up, limit, alpha=1.702, w_bf16=False):
     out = np.empty((T, ff), dtype=np.float32)
     check(lib().xalm_cuda_glu_rows(_p(out), _p(x), _p(w_gate), _p(w_up), T, ff, K, limit, alpha, int(w_bf16)))
     return out
+
+
+def swa_attention_kept(q, k, v, pos0, H, G, d, dv, window, keep_first, scale, ring=None, n_splits=1, cache_bf16=False):
+    """Window attention in which the first keep_first positions stay visible; `ring` = slots behind the keep_first pinned ones."""
+    q, k, v = _f(q), _f(k), _f(v)
+    T = q.shape[0]
+    if ring is None:
+        ring = max(1, min(pos0 + T - keep_first, window - 1 + T))
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_swa_attention_kept(_p(out), _p(q), _p(k), _p(v), T, pos0, H, G, d, dv, window, keep_first, scale, ring, n_splits, int(cache_bf16)))
+    return out
+
+
+def group_norm_residual(y, w, groups, eps, x_in=None, part_w=None, hist=None, dwa=None):
+    """y (T, W) or (T, parts, W).  Returns x_out, or (x_out, depth average) when dwa is given."""
+    y, w, x_in, part_w, hist, dwa = _f(y), _f(w), _f(x_in), _f(part_w), _f(hist), _f(dwa)
+    parts = y.shape[1] if y.ndim == 3 else 1
+    T, W = y.shape[0], y.shape[-1]
+    n_hist = 0 if dwa is None else dwa.shape[0] - 1
+    out, avg = np.empty((T, W), dtype=np.float32), np.empty((T, W), dtype=np.float32)
+    check(lib().xalm_cuda_group_norm_residual(_p(out), _p(avg), _p(y), parts, _pn(part_w), _p(w), groups, eps, _pn(x_in), _pn(hist), n_hist, _pn(dwa), T, W))
+    return out if dwa is None else (out, avg)
+
+
+def qkv_post(proj, pos0, H, G, d, dv, bq=None, bk=None, bv=None, freq=None, norm_qk=True, norm_v=True, eps=1e-5, keep_first=0, ring=None):
+    """Returns (q rows, K cache, V cache) with the caches slot by slot."""
+    proj, bq, bk, bv, freq = _f(proj), _f(bq), _f(bk), _f(bv), _f(freq)
+    T = proj.shape[0]
+    if ring is None:
+        ring = max(1, pos0 + T - keep_first)
+    slots = keep_first + ring
+    q, kc, vc = np.empty((T, H * d), dtype=np.float32), np.empty((slots, G * d), dtype=np.float32), np.empty((slots, G * dv), dtype=np.float32)
+    check(lib().xalm_cuda_qkv_post(_p(q), _p(kc), _p(vc), _p(proj), T, pos0, H, G, d, dv, _pn(bq), _pn(bk), _pn(bv), _pn(freq),
+                                   0 if freq is None else freq.shape[0], int(norm_qk), int(norm_v), eps, keep_first, ring))
+    return q, kc, vc
+
+
+def delta_rule(q, k, v, gate, b, a, state, conv_state, H, G, d, dv, wq, wk, wv, A_log, dt_bias, norm_w=None, eps=1e-5, unit_eps=1e-6, q_scale=None):
+    """Returns (out, new state, new conv_state); the inputs are not modified."""
+    q, k, v, gate, b, a, wq, wk, wv, A_log, dt_bias, norm_w = (_f(x) for x in (q, k, v, gate, b, a, wq, wk, wv, A_log, dt_bias, norm_w))
+    taps = wq.shape[1]
+    st = np.array(state, dtype=np.float32, copy=True)
+    cs = np.array(conv_state, dtype=np.float32, copy=True).reshape(-1)
+    if cs.size == 0:
+        cs = np.zeros(2 * G * d + H * dv, dtype=np.float32)
+    T = q.shape[0]
+    out = np.empty((T, H * dv), dtype=np.float32)
+    check(lib().xalm_cuda_delta_rule(_p(out), _p(st), _p(cs), _p(q), _p(k), _p(v), _p(gate), _p(b), _p(a), T, H, G, d, dv, taps, _p(wq), _p(wk), _p(wv),
+                                     _p(A_log), _p(dt_bias), _pn(norm_w), eps, unit_eps, d ** -0.5 if q_scale is None else q_scale))
+    return out, st, cs.reshape(max(1, taps - 1), -1)[: taps - 1]
+
+
+def moe_ffn(h, w_router, w_gate, w_up, w_down, top, n_groups=0, keep_groups=0, act=1, w_bf16=False):
+    """Returns (idx (T, top), wgt (T, top), out (T, top, K)): the chosen experts, their scores, and each chosen expert's output."""
+    h, w_router, w_gate, w_up, w_down = _f(h), _f(w_router), _f(w_gate), _f(w_up), _f(w_down)
+    T, K = h.shape
+    E, ff = w_gate.shape[0], w_gate.shape[1]
+    idx, wgt, out = np.empty((T, top), dtype=np.int32), np.empty((T, top), dtype=np.float32), np.empty((T, top, K), dtype=np.float32)
+    check(lib().xalm_cuda_moe_ffn(_p(out), _p(idx), _p(wgt), _p(h), _p(w_router), _p(w_gate), _p(w_up), _p(w_down), T, K, E, top, ff, n_groups, keep_groups,
+                                  act, int(w_bf16)))
+    return idx, wgt, out

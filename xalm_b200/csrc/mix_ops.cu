@@ -11,6 +11,8 @@
 #include "common.cuh"
 #include "family.h"
 #include "mix_ops.cuh"
+#include "delta_ops.cuh"
+#include "moe_ops.cuh"
 
 using namespace xalm;
 using namespace xalm::mix;
@@ -56,15 +58,13 @@ uint16_t bf16_bits(float f) {
 
 } // namespace
 
-extern "C" {
-
-int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv,
-                            int window, float scale, float softcap, const float* r1, const float* r2, const float* talk, int ring, int n_splits,
+static int swa_attention_op(float* out, const float* q, const float* gate, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv,
+                            int window, int keep_first, float scale, float softcap, const float* r1, const float* r2, const float* talk, int ring, int n_splits,
                             int cache_bf16) {
-	if (!out || !q || !k || !v || T <= 0 || pos0 < 0 || H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || window <= 0 || n_splits < 1)
+	if (!out || !q || !k || !v || T <= 0 || pos0 < 0 || H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0 || window <= 0 || n_splits < 1 || keep_first < 0)
 		return set_error(XALM_ERR_INVALID, "swa_attention: bad argument");
 	const int n = pos0 + T;
-	const long long need = std::min<long long>(n, (long long) window - 1 + T);
+	const long long need = std::min<long long>(std::max(1, n - keep_first), (long long) window - 1 + T);
 	if (ring < need) return set_error(XALM_ERR_INVALID, "swa_attention: a ring of %d slots cannot hold %lld live positions", ring, need);
 	if (!r1 != !r2) return set_error(XALM_ERR_INVALID, "swa_attention: r1 and r2 come together");
 	const size_t smem = swa_smem_bytes(H, d, dv);
@@ -72,9 +72,10 @@ int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const
 	Pool pool;
 	// the ring as the cache manager leaves it: position p lives in slot p % ring, older positions are overwritten
 	const size_t esz = cache_bf16 ? 2 : 4;
-	std::vector<uint8_t> kr((size_t) ring * G * d * esz, 0), vr((size_t) ring * G * dv * esz, 0);
+	const int slots = keep_first + ring; // the first keep_first positions have slots of their own
+	std::vector<uint8_t> kr((size_t) slots * G * d * esz, 0), vr((size_t) slots * G * dv * esz, 0);
 	for (int p = 0; p < n; p++) {
-		const int slot = p % ring;
+		const int slot = p < keep_first ? p : keep_first + (p - keep_first) % ring;
 		for (int c = 0; c < G * d; c++) {
 			const float x = k[(size_t) p * G * d + c];
 			if (cache_bf16) reinterpret_cast<uint16_t*>(kr.data())[(size_t) slot * G * d + c] = bf16_bits(x);
@@ -94,7 +95,7 @@ int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const
 	a.ldg = H * dv;
 	a.kc = pool.put(kr.data(), kr.size());
 	a.vc = pool.put(vr.data(), vr.size());
-	a.ring = ring; a.H = H; a.G = G; a.d = d; a.dv = dv; a.window = window; a.scale = scale; a.softcap = softcap;
+	a.ring = ring; a.keep_first = keep_first; a.H = H; a.G = G; a.d = d; a.dv = dv; a.window = window; a.scale = scale; a.softcap = softcap;
 	a.r1 = pool.put(r1, (size_t) H); a.r2 = pool.put(r2, (size_t) H); a.talk = pool.put(talk, (size_t) H * H);
 	a.step = pool.put(&st, 1);
 	float* d_out = pool.raw<float>((size_t) T * H * dv);
@@ -108,6 +109,18 @@ int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const
 	XALM_TRY(finish("swa_attention"));
 	XALM_CUDA_CHECK(cudaMemcpy(out, d_out, (size_t) T * H * dv * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;
+}
+
+extern "C" {
+
+int xalm_cuda_swa_attention(float* out, const float* q, const float* gate, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv,
+                            int window, float scale, float softcap, const float* r1, const float* r2, const float* talk, int ring, int n_splits,
+                            int cache_bf16) {
+	return swa_attention_op(out, q, gate, k, v, T, pos0, H, G, d, dv, window, 0, scale, softcap, r1, r2, talk, ring, n_splits, cache_bf16);
+}
+int xalm_cuda_swa_attention_kept(float* out, const float* q, const float* k, const float* v, int T, int pos0, int H, int G, int d, int dv, int window,
+                                 int keep_first, float scale, int ring, int n_splits, int cache_bf16) {
+	return swa_attention_op(out, q, nullptr, k, v, T, pos0, H, G, d, dv, window, keep_first, scale, 0.f, nullptr, nullptr, nullptr, ring, n_splits, cache_bf16);
 }
 
 int xalm_cuda_hgrn2(float* out, float* state, const float* qz, const float* fz, const float* v, int T, int H, int d, int dv, const float* f_bias,
@@ -203,6 +216,152 @@ int xalm_cuda_glu_rows(float* out, const float* x, const float* w_gate, const fl
 	XALM_TRY(launch_rows(d_x, K, d_w, w_bf16 != 0, T, 2 * ff, K, e, nullptr));
 	XALM_TRY(finish("glu_rows"));
 	XALM_CUDA_CHECK(cudaMemcpy(out, e.out, (size_t) T * ff * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_group_norm_residual(float* x_out, float* avg_out, const float* y, int parts, const float* part_w, const float* w, int groups, float eps,
+                                  const float* x_in, const float* hist, int n_hist, const float* dwa, int T, int W) {
+	if (!x_out || !y || !w || parts < 1 || groups < 1 || T <= 0 || W <= 0 || W % groups || (dwa && (!avg_out || (n_hist > 0 && !hist))))
+		return set_error(XALM_ERR_INVALID, "group_norm_residual: bad argument");
+	Pool pool;
+	GroupNormArgs g;
+	g.y = pool.put(y, (size_t) T * parts * W); g.ldy = W; g.parts = parts;
+	g.part_w = pool.put(part_w, (size_t) T * parts);
+	g.w = pool.put(w, (size_t) W); g.groups = groups; g.width = W; g.eps = eps;
+	g.x_in = pool.put(x_in, (size_t) T * W);
+	g.x_out = pool.raw<float>((size_t) T * W);
+	g.hist = pool.put(hist, (size_t) std::max(1, n_hist) * T * W); g.hist_stride = (size_t) T * W; g.n_hist = n_hist;
+	g.dwa = pool.put(dwa, (size_t) n_hist + 1);
+	g.avg_out = dwa ? pool.raw<float>((size_t) T * W) : nullptr;
+	if (!g.y || !g.w || !g.x_out) return set_error(XALM_ERR_CUDA, "group_norm_residual: device allocation failed");
+	XALM_TRY(group_norm_prepare(W, groups));
+	XALM_TRY(launch_group_norm(g, T, nullptr));
+	XALM_TRY(finish("group_norm_residual"));
+	XALM_CUDA_CHECK(cudaMemcpy(x_out, g.x_out, (size_t) T * W * 4, cudaMemcpyDeviceToHost));
+	if (dwa) XALM_CUDA_CHECK(cudaMemcpy(avg_out, g.avg_out, (size_t) T * W * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_qkv_post(float* q_out, float* k_out, float* v_out, const float* proj, int T, int pos0, int H, int G, int d, int dv, const float* bq,
+                       const float* bk, const float* bv, const float* freq, int rot_half, int norm_qk, int norm_v, float eps, int keep_first, int ring) {
+	if (!q_out || !k_out || !v_out || !proj || T <= 0 || pos0 < 0 || H <= 0 || G <= 0 || d <= 0 || dv <= 0 || 2 * rot_half > d || keep_first < 0 || ring < 1)
+		return set_error(XALM_ERR_INVALID, "qkv_post: bad argument");
+	Pool pool;
+	const int ld = H * d + G * d + G * dv, slots = keep_first + ring;
+	const SeqStep st = {pos0, T};
+	QkvPostArgs a = {};
+	a.proj = pool.put(proj, (size_t) T * ld); a.ld = ld; a.q_off = 0; a.k_off = H * d; a.v_off = H * d + G * d;
+	a.H = H; a.G = G; a.d = d; a.dv = dv;
+	a.bq = pool.put(bq, (size_t) H * d); a.bk = pool.put(bk, (size_t) G * d); a.bv = pool.put(bv, (size_t) G * dv);
+	a.freq = rot_half ? pool.put(freq, (size_t) rot_half) : nullptr; a.rot_half = rot_half;
+	a.norm_qk = norm_qk; a.norm_v = norm_v; a.eps = eps;
+	float* kc = pool.raw<float>((size_t) slots * G * d);
+	float* vc = pool.raw<float>((size_t) slots * G * dv);
+	a.kc = kc; a.vc = vc; a.cache_f32 = 1; a.keep_first = keep_first; a.ring = ring;
+	a.step = pool.put(&st, 1);
+	if (!a.proj || !kc || !vc || !a.step) return set_error(XALM_ERR_CUDA, "qkv_post: device allocation failed");
+	XALM_TRY(launch_qkv_post(a, T, nullptr));
+	XALM_TRY(finish("qkv_post"));
+	std::vector<float> back((size_t) T * ld);
+	XALM_CUDA_CHECK(cudaMemcpy(back.data(), a.proj, back.size() * 4, cudaMemcpyDeviceToHost));
+	for (int t = 0; t < T; t++) memcpy(q_out + (size_t) t * H * d, &back[(size_t) t * ld], (size_t) H * d * 4);
+	// the whole cache, slot by slot, so that a test sees where each position went
+	XALM_CUDA_CHECK(cudaMemcpy(k_out, kc, (size_t) slots * G * d * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(v_out, vc, (size_t) slots * G * dv * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_delta_rule(float* out, float* state, float* conv_state, const float* q, const float* k, const float* v, const float* gate, const float* b,
+                         const float* a_in, int T, int H, int G, int d, int dv, int taps, const float* wq, const float* wk, const float* wv,
+                         const float* A_log, const float* dt_bias, const float* norm_w, float eps, float unit_eps, float q_scale) {
+	if (!out || !state || !conv_state || !q || !k || !v || !gate || !b || !a_in || !wq || !wk || !wv || !A_log || !dt_bias || T <= 0 || H <= 0 || G <= 0 || H % G ||
+	    d <= 0 || dv <= 0 || taps < 1)
+		return set_error(XALM_ERR_INVALID, "delta_rule: bad argument");
+	if (!delta_ok(d, dv)) return set_error(XALM_ERR_UNSUPPORTED, "delta_rule: a state of %d x %d per head", d, dv);
+	Pool pool;
+	const int nq = G * d, nv = H * dv, Cc = 2 * nq + nv, ld = Cc + nv + 2 * H;
+	std::vector<float> proj((size_t) T * ld);
+	for (int t = 0; t < T; t++) {
+		float* row = &proj[(size_t) t * ld];
+		memcpy(row, q + (size_t) t * nq, (size_t) nq * 4);
+		memcpy(row + nq, k + (size_t) t * nq, (size_t) nq * 4);
+		memcpy(row + 2 * nq, v + (size_t) t * nv, (size_t) nv * 4);
+		memcpy(row + Cc, gate + (size_t) t * nv, (size_t) nv * 4);
+		memcpy(row + Cc + nv, b + (size_t) t * H, (size_t) H * 4);
+		memcpy(row + Cc + nv + H, a_in + (size_t) t * H, (size_t) H * 4);
+	}
+	const SeqStep st = {0, T};
+	DeltaArgs a = {};
+	a.proj = pool.put(proj.data(), proj.size()); a.ld = ld;
+	a.q_off = 0; a.k_off = nq; a.v_off = 2 * nq; a.g_off = Cc; a.b_off = Cc + nv; a.a_off = Cc + nv + H;
+	a.H = H; a.G = G; a.d = d; a.dv = dv; a.taps = taps;
+	a.wq = pool.put(wq, (size_t) nq * taps); a.wk = pool.put(wk, (size_t) nq * taps); a.wv = pool.put(wv, (size_t) nv * taps);
+	a.A_log = pool.put(A_log, (size_t) H); a.dt_bias = pool.put(dt_bias, (size_t) H); a.norm_w = pool.put(norm_w, (size_t) dv);
+	a.eps = eps; a.unit_eps = unit_eps; a.q_scale = q_scale;
+	const size_t ncs = (size_t) std::max(1, taps - 1) * Cc;
+	a.conv_state = pool.put(conv_state, ncs);
+	a.state = pool.put(state, (size_t) H * d * dv);
+	a.ldp = Cc + 2 * H;
+	a.prep = pool.raw<float>((size_t) T * a.ldp);
+	a.out = pool.raw<float>((size_t) T * nv);
+	a.step = pool.put(&st, 1);
+	if (!a.proj || !a.conv_state || !a.state || !a.prep || !a.out || !a.step) return set_error(XALM_ERR_CUDA, "delta_rule: device allocation failed");
+	XALM_TRY(delta_prepare(d, dv));
+	XALM_TRY(launch_delta(a, T, nullptr));
+	XALM_TRY(finish("delta_rule"));
+	XALM_CUDA_CHECK(cudaMemcpy(out, a.out, (size_t) T * nv * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(state, a.state, (size_t) H * d * dv * 4, cudaMemcpyDeviceToHost));
+	if (taps > 1) XALM_CUDA_CHECK(cudaMemcpy(conv_state, a.conv_state, ncs * 4, cudaMemcpyDeviceToHost));
+	return XALM_OK;
+}
+
+int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, const float* w_router, const float* w_gate, const float* w_up,
+                      const float* w_down, int T, int K, int E, int top, int ff, int n_groups, int keep_groups, int act, int w_bf16) {
+	if (!out_pairs || !idx || !wgt || !h || !w_router || !w_gate || !w_up || !w_down || T <= 0 || K <= 0 || E <= 0 || top <= 0 || ff <= 0)
+		return set_error(XALM_ERR_INVALID, "moe_ffn: bad argument");
+	Pool pool;
+	// gate and up rows interleaved expert after expert, as the families store them
+	std::vector<float> gu((size_t) E * 2 * ff * K);
+	for (int e = 0; e < E; e++)
+		for (int i = 0; i < ff; i++) {
+			memcpy(&gu[((size_t) e * 2 * ff + 2 * i) * K], w_gate + ((size_t) e * ff + i) * K, (size_t) K * 4);
+			memcpy(&gu[((size_t) e * 2 * ff + 2 * i + 1) * K], w_up + ((size_t) e * ff + i) * K, (size_t) K * 4);
+		}
+	auto put_w = [&](const float* src, size_t n) -> void* {
+		if (!w_bf16) return pool.put(src, n);
+		std::vector<uint16_t> wb(n);
+		for (size_t i = 0; i < n; i++) wb[i] = bf16_bits(src[i]);
+		return pool.put(wb.data(), n);
+	};
+	const SeqStep st = {0, T};
+	const SeqStep* d_st = pool.put(&st, 1);
+	const int P = T * top, max_tiles = moe_max_tiles(P, E);
+	MoeRouteArgs ra = {};
+	ra.h = pool.put(h, (size_t) T * K); ra.ldh = K; ra.w = put_w(w_router, (size_t) E * K); ra.w_bf16 = w_bf16;
+	ra.E = E; ra.top = top; ra.K = K; ra.n_groups = n_groups; ra.keep_groups = keep_groups;
+	ra.idx = pool.raw<int>((size_t) P); ra.wgt = pool.raw<float>((size_t) P); ra.step = d_st;
+	MoeSortArgs so = {ra.idx, top, E, d_st, pool.raw<int>((size_t) P), pool.raw<int>((size_t) 3 * max_tiles), pool.raw<int>(1)};
+	MoeGemmArgs ga = {};
+	ga.A = ra.h; ga.lda = K; ga.a_div = top; ga.W = put_w(gu.data(), gu.size()); ga.N = 2 * ff; ga.K = K;
+	ga.sorted = so.sorted; ga.tiles = so.tiles; ga.n_tiles = so.n_tiles;
+	float* hid = pool.raw<float>((size_t) P * ff);
+	float* outp = pool.raw<float>((size_t) P * K);
+	ga.e.kind = EPI_GLU; ga.e.glu_act = act; ga.e.out = hid; ga.e.ldo = ff; ga.e.limit = INFINITY;
+	void* d_down = put_w(w_down, (size_t) E * K * ff);
+	if (!d_st || !ra.h || !ra.w || !ra.idx || !ra.wgt || !so.sorted || !so.tiles || !so.n_tiles || !ga.W || !hid || !outp || !d_down)
+		return set_error(XALM_ERR_CUDA, "moe_ffn: device allocation failed");
+	XALM_TRY(moe_prepare(K, E, n_groups));
+	XALM_TRY(launch_moe_router(ra, T, nullptr));
+	XALM_TRY(launch_moe_sort(so, nullptr));
+	XALM_TRY(launch_moe_gemm(ga, w_bf16 != 0, P, E, nullptr));
+	ga.A = hid; ga.lda = ff; ga.a_div = 1; ga.W = d_down; ga.N = K; ga.K = ff;
+	ga.e = RowsEpi();
+	ga.e.kind = EPI_STORE; ga.e.out = outp; ga.e.ldo = K;
+	XALM_TRY(launch_moe_gemm(ga, w_bf16 != 0, P, E, nullptr));
+	XALM_TRY(finish("moe_ffn"));
+	XALM_CUDA_CHECK(cudaMemcpy(out_pairs, outp, (size_t) P * K * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(idx, ra.idx, (size_t) P * 4, cudaMemcpyDeviceToHost));
+	XALM_CUDA_CHECK(cudaMemcpy(wgt, ra.wgt, (size_t) P * 4, cudaMemcpyDeviceToHost));
 	return XALM_OK;
 }
 

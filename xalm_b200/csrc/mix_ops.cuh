@@ -15,6 +15,8 @@
 //   hgrn2_kernel           gated linear recurrence S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t with a lower-bounded
 //                          forget gate, state in fp32 carried in device memory, per-head RMS norm of o fused
 //   dual_norm_hc_kernel    y = 1/2 (rmsnorm(a) wa + rmsnorm(b) wb) -> layer scale -> hyper-connection write
+//   group_norm_residual_kernel  x + grouped RMS norm of a sublayer's output (weighted sum of expert rows first), depth-weighted average
+//   qkv_post_kernel        bias, rotary positions, weightless RMS norms of q / k / v heads, K/V cache write (kept first slots + ring)
 //
 // The kernels have internal linkage: every translation unit that includes this header (a model family, the op-level entry points
 // of mix_ops.cu) gets its own copies.
@@ -151,6 +153,7 @@ __global__ void hc_norm_kernel(const float* __restrict__ xs, int S, size_t strea
 
 // ---- fused epilogues of the row products -------------------------------------------------------------------------------------
 enum { EPI_STORE = 0, EPI_SPLIT_KV = 1, EPI_GLU = 2, EPI_HC = 3 };
+enum { GLU_CLAMPED = 0, GLU_SILU = 1, GLU_GELU_TANH = 2 };
 struct RowsEpi {
 	int kind = EPI_STORE;
 	float* out = nullptr; // STORE / SPLIT_KV: (T, ldo); GLU: (T, ldo) with ldo = N / 2
@@ -165,8 +168,10 @@ struct RowsEpi {
 	int silu_off = 0, silu_n = 0, gate_off = 0, gate_n = 0;
 	const float* gate_bias = nullptr;
 	const float* gate_lower = nullptr;
-	// GLU: even column = gate, odd = up: y = min(g, limit) * sigmoid(alpha * .) * (clamp(u, +-limit) + 1)
+	// GLU: even column = gate, odd = up.  glu_act GLU_CLAMPED: y = min(g, limit) * sigmoid(alpha * .) * (clamp(u, +-limit) + 1);
+	// GLU_SILU: y = g sigmoid(g) u;  GLU_GELU_TANH: y = 1/2 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u
 	float limit = 0.f, alpha = 1.702f;
+	int glu_act = 0;
 	// HC: xs[t'][row][col] = sum_s hmix[s * S + t'] xs[s][row][col] + hout[t'] * scale[col] * value   (hmix / hout NULL: identity / ones)
 	float* xs = nullptr;
 	int S = 1;
@@ -180,6 +185,13 @@ __device__ __forceinline__ float glu_clamped(float g, float u, float limit, floa
 	g = fminf(g, limit);
 	u = fminf(fmaxf(u, -limit), limit);
 	return g * sigmoidf_(alpha * g) * (u + 1.f);
+}
+
+__device__ __forceinline__ float gelu_tanhf_(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float glu_apply(int act, float g, float u, float limit, float alpha) {
+	if (act == GLU_SILU) return g * sigmoidf_(g) * u;
+	if (act == GLU_GELU_TANH) return gelu_tanhf_(g) * u;
+	return glu_clamped(g, u, limit, alpha);
 }
 
 __device__ __forceinline__ void hc_write(const RowsEpi& e, int row, int col, int width, float v) {
@@ -224,7 +236,7 @@ __device__ __forceinline__ void epi_apply(const RowsEpi& e, int row, int col, in
 			}
 			break;
 		}
-		case EPI_GLU: e.out[(size_t) row * e.ldo + (col >> 1)] = glu_clamped(v, v_next, e.limit, e.alpha); break;
+		case EPI_GLU: e.out[(size_t) row * e.ldo + (col >> 1)] = glu_apply(e.glu_act, v, v_next, e.limit, e.alpha); break;
 		case EPI_HC: hc_write(e, row, col, N, v); break;
 	}
 }
@@ -378,6 +390,8 @@ struct SwaArgs {
 	int ring;
 	int H, G, d, dv;
 	int window;        // position i sees j with 0 <= i - j < window
+	int keep_first;    // ... and every j < keep_first (j <= i) however far back: the sequence's first positions stay visible at their true
+	                   // places.  They live in slots [0, keep_first) of the cache, the others in the `ring` slots behind (0: a plain ring)
 	float scale;
 	float softcap;     // 0: none
 	const float* r1;   // distance bias r1[h] * log1p(r2[h] * (i - j)) taken off the score; NULL: none
@@ -397,6 +411,25 @@ struct SwaArgs {
 };
 
 constexpr int SWA_KB = 32; // keys per block
+
+// The keys a CTA's queries [i_lo, i_hi] can see, as one run of "virtual" indices: first the kept positions that have left the window of
+// i_lo, then the positions from the window's start on.  pos(): the position in the sequence; slot(): where the cache keeps it.
+struct SwaKeys {
+	int j_first, ks, keep, ring;
+	__device__ __forceinline__ int pos(int v) const { return v < ks ? v : j_first + (v - ks); }
+	__device__ __forceinline__ int slot(int v) const {
+		const int j = pos(v);
+		return j < keep ? j : keep + (j - keep) % ring;
+	}
+};
+__device__ __forceinline__ SwaKeys swa_keys(int window, int keep_first, int ring, int i_lo) {
+	SwaKeys k;
+	k.j_first = window < 0x7fffffff ? max(0, i_lo - window + 1) : 0;
+	k.ks = min(keep_first, k.j_first);
+	k.keep = keep_first;
+	k.ring = ring;
+	return k;
+}
 
 // joins the key splits of rows [t_first, t_first + rows): out = (sum_s e^{m_s - m} O_s) / (sum_s e^{m_s - m} l_s), then the gate
 __device__ __forceinline__ void swa_merge_one(const SwaArgs& a, int t, int hc) {
@@ -480,11 +513,11 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 	const bool vec8 = ((d | (G * d)) & 7) == 0;
 	if (t >= a.step->n) return;
 	const int i = a.step->pos0 + t;
-	const int j_first = max(0, i - a.window + 1);
-	const int nk = i - j_first + 1;
+	const SwaKeys km = swa_keys(a.window, a.keep_first, a.ring, i);
+	const int nk = km.ks + i - km.j_first + 1; // every one of them is visible to this query
 	int per = (nk + a.n_splits - 1) / a.n_splits;
 	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
-	const int jb = j_first + sp * per, je = min(i + 1, jb + per);
+	const int jb = sp * per, je = min(nk, jb + per); // virtual key indices
 	// staged rows: Ks[jj][G d], Vs[jj][G dv] in the cache's element type
 	const bool staged = a.stage_off > 0;
 	CT* Ks = reinterpret_cast<CT*>(sm + a.stage_off);
@@ -495,12 +528,12 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 		for (int x = tid; x < nb * kch; x += nth) {
 			const int jj = x / kch, c = (x % kch) * EPC;
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Ks + (size_t) jj * (G * d) + c);
-			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) ((j0 + jj) % a.ring) * (G * d) + c) : "memory");
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + (size_t) km.slot(j0 + jj) * (G * d) + c) : "memory");
 		}
 		for (int x = tid; x < nb * vch; x += nth) {
 			const int jj = x / vch, c = (x % vch) * EPC;
 			const unsigned dst = (unsigned) __cvta_generic_to_shared(Vs + (size_t) jj * (G * dv) + c);
-			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) ((j0 + jj) % a.ring) * (G * dv) + c) : "memory");
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vc + (size_t) km.slot(j0 + jj) * (G * dv) + c) : "memory");
 		}
 		asm volatile("cp.async.commit_group;" ::: "memory");
 	};
@@ -539,7 +572,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 #pragma unroll
 					for (int kq = 0; kq < 4; kq++) {
 						const int jj = warp + kq * 8;
-						const CT* kr = (staged ? Ks + (size_t) jj * (G * d) : kc + (size_t) ((j0 + jj) % a.ring) * (G * d)) + g * d + c;
+						const CT* kr = (staged ? Ks + (size_t) jj * (G * d) : kc + (size_t) km.slot(j0 + min(jj, nb - 1)) * (G * d)) + g * d + c;
 						if (jj < nb && vec8) ld8(kr, kk[kq]);
 						else
 #pragma unroll
@@ -570,7 +603,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 						if (lane == kq * 4 + u) mine = tot;
 					}
 				if (lane < 16) {
-					const int kq = lane >> 2, u = lane & 3, jj = warp + kq * 8, j = j0 + jj;
+					const int kq = lane >> 2, u = lane & 3, jj = warp + kq * 8, j = km.pos(j0 + jj);
 					if (u < nh) {
 						const int h = g * rep + hr + u;
 						float sv = 0.f;
@@ -625,7 +658,7 @@ __global__ void __launch_bounds__(256) swa_attn_kernel(SwaArgs a) {
 				for (int jb8 = 0; jb8 < nb; jb8 += 8) { // eight loads in flight
 					float v[8];
 #pragma unroll
-					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) (staged ? jb8 + e8 : (j0 + jb8 + e8) % a.ring) * (G * dv)) : 0.f;
+					for (int e8 = 0; e8 < 8; e8++) v[e8] = jb8 + e8 < nb ? ldf(vcol + (size_t) (staged ? jb8 + e8 : km.slot(j0 + jb8 + e8)) * (G * dv)) : 0.f;
 #pragma unroll
 					for (int e8 = 0; e8 < 8; e8++)
 #pragma unroll
@@ -693,7 +726,7 @@ __host__ __device__ inline size_t swa_tile_smem_floats(int H, int G, int d, int 
 // rows j0 .. j0 + SWA_KB of one kv group's slice of the ring (w elements at column col0 of rows of row_elems) -> dst[jj * ldd + c] in fp32,
 // zero beyond nbk rows and beyond w columns (up to wp).  16-byte loads, two in flight per thread, when the slice allows.
 template <typename CT>
-__device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* base, int row_elems, int col0, int w, int wp, int j0, int nbk, int ring,
+__device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* base, int row_elems, int col0, int w, int wp, int j0, int nbk, const SwaKeys& km,
                                               int tid, int nth) {
 	if (((w | row_elems | col0) & 7) == 0) {
 		const int cpr = w >> 3, total = SWA_KB * cpr;
@@ -702,7 +735,7 @@ __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* bas
 #pragma unroll
 			for (int u = 0; u < 2; u++) {
 				const int x = x0 + u * nth, jj = x / cpr, c = (x % cpr) << 3;
-				if (x < total && jj < nbk) ld8(base + (size_t) ((j0 + jj) % ring) * row_elems + col0 + c, v[u]);
+				if (x < total && jj < nbk) ld8(base + (size_t) km.slot(j0 + jj) * row_elems + col0 + c, v[u]);
 				else
 #pragma unroll
 					for (int i = 0; i < 8; i++) v[u][i] = 0.f;
@@ -719,7 +752,7 @@ __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* bas
 	} else {
 		for (int x = tid; x < SWA_KB * wp; x += nth) {
 			const int jj = x / wp, k = x % wp;
-			dst[jj * ldd + k] = (jj < nbk && k < w) ? ldf(base + (size_t) ((j0 + jj) % ring) * row_elems + col0 + k) : 0.f;
+			dst[jj * ldd + k] = (jj < nbk && k < w) ? ldf(base + (size_t) km.slot(j0 + jj) * row_elems + col0 + k) : 0.f;
 		}
 	}
 }
@@ -728,7 +761,7 @@ __device__ __forceinline__ void swa_load_tile(float* dst, int ldd, const CT* bas
 // tile with few rows per group still has work for every thread; then scale, soft cap, distance bias -> Sc[key][row]
 template <int KT, int RT>
 __device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, const float* KV, float* Sc, int g, int Rg, int R, int ldq, int ldkv, int dp,
-                                             int TQ, int rep, int nq, int nbk, int i_lo, int j0, int tid, int nth) {
+                                             int TQ, int rep, int nq, int nbk, int i_lo, int j0, const SwaKeys& km, int tid, int nth) {
 	constexpr int NTK = SWA_KB / KT;
 	for (int tile = tid; tile < (Rg / RT) * NTK; tile += nth) {
 		const int mt = tile / NTK, nt = tile % NTK;
@@ -753,7 +786,7 @@ __device__ __forceinline__ void swa_qk_tiles(const SwaArgs& a, const float* Qs, 
 		}
 #pragma unroll
 		for (int u = 0; u < KT; u++) {
-			const int jj = nt + NTK * u, j = j0 + jj;
+			const int jj = nt + NTK * u, j = km.pos(j0 + jj);
 			float o4[RT];
 #pragma unroll
 			for (int i = 0; i < RT; i++) {
@@ -834,11 +867,11 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 	const int nq = min(TQ, n - t0);          // queries of this tile (<= 0: nothing to do)
 	if (nq <= 0) return;
 	const int i_lo = pos0 + t0, i_hi = i_lo + nq - 1;
-	const int j_first = a.window < 0x7fffffff ? max(0, i_lo - a.window + 1) : 0;
-	const int nk = i_hi - j_first + 1;
+	const SwaKeys km = swa_keys(a.window, a.keep_first, a.ring, i_lo);
+	const int nk = km.ks + i_hi - km.j_first + 1;
 	int per = (nk + a.n_splits - 1) / a.n_splits;
 	per = (per + SWA_KB - 1) / SWA_KB * SWA_KB;
-	const int jb = j_first + sp * per, je = min(i_hi + 1, jb + per);
+	const int jb = sp * per, je = min(nk, jb + per); // virtual key indices
 
 	// ---- Q tile (zero rows where the tile has no head or no query), constants ----
 	for (int x = tid; x < R * (dp >> 2); x += nth) {
@@ -866,12 +899,12 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- raw scores, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // the last reader of KV (and, on the first pass, the set-up above) is done
-			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, a.ring, tid, nth);
+			swa_load_tile(KV, ldkv, kc, G * d, g * d, d, dp, j0, nbk, km, tid, nth);
 			__syncthreads();
-			if (kt == 4) swa_qk_tiles<4, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
-			else if (kt == 2) swa_qk_tiles<2, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
-			else if ((Rg >> 2) * SWA_KB >= nth) swa_qk_tiles<1, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
-			else swa_qk_tiles<1, 2>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, tid, nth);
+			if (kt == 4) swa_qk_tiles<4, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
+			else if (kt == 2) swa_qk_tiles<2, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
+			else if ((Rg >> 2) * SWA_KB >= nth) swa_qk_tiles<1, 4>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
+			else swa_qk_tiles<1, 2>(a, Qs, KV, Sc, g, Rg, R, ldq, ldkv, dp, TQ, rep, nq, nbk, i_lo, j0, km, tid, nth);
 		}
 		__syncthreads();
 		// ---- mix the heads' scores (4 output heads per thread), mask ----
@@ -879,13 +912,20 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 			const int hq = x % (Hp >> 2), rest = x / (Hp >> 2), q = rest % TQ, jj = rest / TQ;
 			float m4[4] = {0.f, 0.f, 0.f, 0.f};
 			const float* srow = Sc + (size_t) jj * R + q;
+			if (!a.talk) { // no mixing: every head keeps its own score
+#pragma unroll
+				for (int u = 0; u < 4; u++) {
+					const int h = min(4 * hq + u, H - 1);
+					m4[u] = srow[(h / rep) * Rg + (h % rep) * TQ];
+				}
+			} else
 			for (int g = 0; g < H; g++) {
 				const float s = srow[(g / rep) * Rg + (g % rep) * TQ];
 				const float4 w = *reinterpret_cast<const float4*>(tkT + g * Hp + 4 * hq);
 				m4[0] = fmaf(w.x, s, m4[0]); m4[1] = fmaf(w.y, s, m4[1]); m4[2] = fmaf(w.z, s, m4[2]); m4[3] = fmaf(w.w, s, m4[3]);
 			}
-			const int i = i_lo + q, j = j0 + jj;
-			const bool seen = q < nq && jj < nbk && j <= i && (a.window >= 0x7fffffff || i - j < a.window);
+			const int i = i_lo + q, j = km.pos(j0 + jj);
+			const bool seen = q < nq && jj < nbk && j <= i && (a.window >= 0x7fffffff || i - j < a.window || j < a.keep_first);
 #pragma unroll
 			for (int u = 0; u < 4; u++) {
 				const int h = 4 * hq + u;
@@ -912,7 +952,7 @@ __global__ void __launch_bounds__(256) swa_tile_kernel(SwaArgs a) {
 		// ---- O <- alpha O + P^T V, one kv group at a time ----
 		for (int g = 0; g < G; g++) {
 			__syncthreads(); // probabilities written; the last reader of KV is done
-			swa_load_tile(KV, ldkv, vc, G * dv, g * dv, dv, dvp, j0, nbk, a.ring, tid, nth);
+			swa_load_tile(KV, ldkv, vc, G * dv, g * dv, dv, dvp, j0, nbk, km, tid, nth);
 			__syncthreads();
 			if ((Rg >> 2) * (dvp >> 2) >= nth) swa_pv_tiles<4>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
 			else swa_pv_tiles<2>(Pr, KV, O, alpha, g, Rg, R, ldkv, dvp, tid, nth);
@@ -1344,6 +1384,152 @@ static inline int hgrn2_prepare(int d, int dv) {
 	return XALM_OK;
 }
 
+// ---- grouped RMS norm of a sublayer's output, residual add, depth-weighted average ------------------------------------------------
+// For designs that norm what a sublayer returns and not what it reads:  v = x_in + gnorm(y) * w, where gnorm splits the row into
+// `groups` equal consecutive parts and divides each by its own sqrt(mean(part^2) + eps).  Along for the ride, because each is one more
+// pass over the same row otherwise:
+//   * y may come in `parts` rows per token that are first summed with weights part_w (the chosen experts of a mixture, in slot order:
+//     a fixed order, so the sum is the same bits every run);
+//   * the depth-weighted average: with hist holding the earlier layers' results X_0 .. X_{n_hist-1} for this pass and v being X_{n_hist},
+//     avg_out = sum_j dwa[j] X_j is what the next layer reads;
+//   * keep_out: a copy of what goes on to the next layer, for readers outside the model.
+struct GroupNormArgs {
+	const float* y = nullptr;      // (rows * parts, ldy)
+	int ldy = 0, parts = 1;
+	const float* part_w = nullptr; // (rows, parts), or NULL: parts == 1 with weight 1
+	const float* w = nullptr;      // (width)
+	int groups = 1, width = 0;
+	float eps = 1e-5f;
+	const float* x_in = nullptr;   // (rows, width) or NULL: no residual (the model's final norm)
+	float* x_out = nullptr;        // (rows, width); may be x_in
+	const float* hist = nullptr;   // (n_hist, hist_stride) earlier results of this pass, or NULL
+	size_t hist_stride = 0;
+	int n_hist = 0;
+	const float* dwa = nullptr;    // (n_hist + 1)
+	float* avg_out = nullptr;      // (rows, width)
+	float* keep_out = nullptr;     // (rows, width) or NULL
+};
+static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
+	extern __shared__ float sm[];
+	float* u = sm;               // width
+	float* rinv = sm + a.width;  // groups
+	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
+	const int W = a.width, gs = W / a.groups;
+	for (int c = tid; c < W; c += nth) {
+		float v;
+		if (a.part_w) {
+			v = 0.f;
+			for (int k = 0; k < a.parts; k++) v = fmaf(a.part_w[(size_t) t * a.parts + k], a.y[((size_t) t * a.parts + k) * a.ldy + c], v);
+		} else v = a.y[(size_t) t * a.ldy + c];
+		u[c] = v;
+	}
+	__syncthreads();
+	for (int g = warp; g < a.groups; g += nw) {
+		float ss = 0.f;
+		for (int c = lane; c < gs; c += 32) ss = fmaf(u[g * gs + c], u[g * gs + c], ss);
+		ss = warp_sum(ss);
+		if (lane == 0) rinv[g] = 1.f / sqrtf(ss / (float) gs + a.eps);
+	}
+	__syncthreads();
+	for (int c = tid; c < W; c += nth) {
+		const size_t at = (size_t) t * W + c;
+		float v = u[c] * rinv[c / gs] * a.w[c];
+		if (a.x_in) v += a.x_in[at];
+		a.x_out[at] = v;
+		if (a.dwa) {
+			float s = 0.f;
+			for (int j = 0; j < a.n_hist; j++) s = fmaf(a.dwa[j], a.hist[(size_t) j * a.hist_stride + at], s);
+			v = fmaf(a.dwa[a.n_hist], v, s);
+			a.avg_out[at] = v;
+		}
+		if (a.keep_out) a.keep_out[at] = v;
+	}
+}
+static inline size_t group_norm_smem(int width, int groups) { return (size_t) (width + groups) * 4; }
+static inline int group_norm_prepare(int width, int groups) {
+	static bool raised = false;
+	if (group_norm_smem(width, groups) > 48 * 1024 && !raised) {
+		XALM_CUDA_CHECK(cudaFuncSetAttribute(group_norm_residual_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+		raised = true;
+	}
+	return XALM_OK;
+}
+static inline int launch_group_norm(const GroupNormArgs& a, int rows, cudaStream_t s) {
+	if (a.groups <= 0 || a.width % a.groups) return set_error(XALM_ERR_INVALID, "group norm: %d groups do not divide a row of %d", a.groups, a.width);
+	group_norm_residual_kernel<<<rows, norm_threads(a.width), group_norm_smem(a.width, a.groups), s>>>(a);
+	return launch_check("group_norm_residual");
+}
+
+// ---- after the q | k | v projection of an attention layer: bias, rotary positions, RMS norms without weight, cache write ------------
+// One warp per head of a token.  Query heads are rewritten in place; key and value heads go to the cache slot of the token's position
+// (SwaKeys layout: the first keep_first positions in slots of their own, the rest in a ring).  Rotation: the first 2 * rot_half
+// dimensions of a query / key head, dimension i paired with i + rot_half, angle = position * freq[i] in fp32 (sincosf).  The norms
+// (x / sqrt(mean(x^2) + eps) over the head, no weight) come after the rotation; each is optional.
+struct QkvPostArgs {
+	float* proj; // (T, ld)
+	int ld, q_off, k_off, v_off;
+	int H, G, d, dv;
+	const float *bq, *bk, *bv; // biases of the three projections, or NULL
+	const float* freq;         // (rot_half) or NULL
+	int rot_half;
+	int norm_qk, norm_v;
+	float eps;
+	void *kc, *vc;
+	int cache_f32, keep_first, ring;
+	const SeqStep* step;
+};
+static __global__ void qkv_post_kernel(QkvPostArgs a) {
+	extern __shared__ float sm[];
+	const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+	const int unit = blockIdx.y * nw + warp;
+	if (t >= a.step->n || unit >= a.H + 2 * a.G) return;
+	const int wmax = a.d > a.dv ? a.d : a.dv;
+	float* x = sm + (size_t) warp * wmax;
+	const int pos = a.step->pos0 + t;
+	const int kind = unit < a.H ? 0 : unit < a.H + a.G ? 1 : 2; // q, k, v
+	const int hd = kind == 0 ? unit : kind == 1 ? unit - a.H : unit - a.H - a.G;
+	const int n = kind == 2 ? a.dv : a.d;
+	float* src = a.proj + (size_t) t * a.ld + (kind == 0 ? a.q_off : kind == 1 ? a.k_off : a.v_off) + hd * n;
+	const float* bias = kind == 0 ? a.bq : kind == 1 ? a.bk : a.bv;
+	for (int c = lane; c < n; c += 32) x[c] = src[c] + (bias ? bias[hd * n + c] : 0.f);
+	__syncwarp();
+	if (kind != 2 && a.freq) {
+		const int r = a.rot_half;
+		for (int c = lane; c < r; c += 32) {
+			float sn, cs;
+			sincosf((float) pos * a.freq[c], &sn, &cs);
+			const float p = x[c], q = x[c + r];
+			x[c] = p * cs - q * sn;
+			x[c + r] = q * cs + p * sn;
+		}
+		__syncwarp();
+	}
+	float rs = 1.f;
+	if (kind == 2 ? a.norm_v : a.norm_qk) {
+		float ss = 0.f;
+		for (int c = lane; c < n; c += 32) ss = fmaf(x[c], x[c], ss);
+		ss = warp_sum(ss);
+		rs = 1.f / sqrtf(ss / (float) n + a.eps);
+	}
+	if (kind == 0) {
+		for (int c = lane; c < n; c += 32) src[c] = x[c] * rs;
+		return;
+	}
+	const int slot = pos < a.keep_first ? pos : a.keep_first + (pos - a.keep_first) % a.ring;
+	const size_t at = ((size_t) slot * a.G + hd) * n;
+	void* cache = kind == 1 ? a.kc : a.vc;
+	if (a.cache_f32)
+		for (int c = lane; c < n; c += 32) ((float*) cache)[at + c] = x[c] * rs;
+	else
+		for (int c = lane; c < n; c += 32) ((__nv_bfloat16*) cache)[at + c] = __float2bfloat16_rn(x[c] * rs);
+}
+static inline int launch_qkv_post(const QkvPostArgs& a, int rows, cudaStream_t s) {
+	const int units = a.H + 2 * a.G, nw = units < 8 ? units : 8, wmax = a.d > a.dv ? a.d : a.dv;
+	if ((size_t) nw * wmax * 4 > 48 * 1024) return set_error(XALM_ERR_UNSUPPORTED, "qkv_post: heads of %d do not fit shared memory", wmax);
+	qkv_post_kernel<<<dim3(rows, (units + nw - 1) / nw), nw * 32, (size_t) nw * wmax * 4, s>>>(a);
+	return launch_check("qkv_post");
+}
+
 static inline int launch_rows_epilogue(const float* src, int lds, int T, int N, const RowsEpi& e, cudaStream_t s) {
 	const size_t total = (size_t) T * (e.kind == EPI_GLU ? (N + 1) / 2 : N);
 	rows_epilogue_kernel<<<(int) std::min<size_t>((total + 255) / 256, 148 * 16), 256, 0, s>>>(src, lds, T, N, e);
@@ -1394,7 +1580,7 @@ static inline int launch_swa(SwaArgs a, int rows, bool cache_f32, cudaStream_t s
 	const int tq = swa_pick_tq(a.H, a.G, a.d, a.dv, rows);
 	if (a.n_splits <= 0) { // enough CTAs for two waves, at least two key blocks each
 		const int qblocks = tq ? (rows + tq - 1) / tq : rows;
-		const long long keys = std::min<long long>((long long) a.ring, (long long) (a.window < 0x7fffffff ? a.window : a.ring) + (tq ? tq : 1));
+		const long long keys = std::min<long long>((long long) a.ring, (long long) (a.window < 0x7fffffff ? a.window : a.ring) + (tq ? tq : 1)) + a.keep_first;
 		int want = std::max(1, 296 / std::max(1, qblocks));
 		want = (int) std::min<long long>(want, std::max<long long>(1, tq ? keys / (2 * SWA_KB) : (keys + SWA_KB - 1) / SWA_KB)); // key blocks per CTA: >= 2 (tiled), 1 (one query)
 		a.n_splits = (a.part_o && a.part_ml) ? std::max(1, std::min(want, a.part_cap / std::max(1, rows))) : 1;
