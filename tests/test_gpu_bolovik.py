@@ -46,7 +46,7 @@ def test_group_norm_residual_and_depth_average(W, groups):
 @pytest.mark.parametrize("H,G,d,dv,rot_dims", [(4, 2, 8, 12, 4), (3, 3, 16, 4, 16), (6, 1, 20, 20, 0), (1, 1, 64, 8, 32), (2, 2, 6, 3, 2)])
 def test_qkv_post_rotation_norms_and_slots(H, G, d, dv, rot_dims):
     rng = np.random.default_rng(H * d + rot_dims)
-    T, pos0, keep, ring = 9, 1000, 3, 7
+    T, pos0, keep, ring = 6, 1000, 3, 7
     proj = rng.standard_normal((T, H * d + G * d + G * dv)) * 2
     bq, bk, bv = rng.standard_normal(H * d), rng.standard_normal(G * d), rng.standard_normal(G * dv)
     scaling = {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}
@@ -57,11 +57,10 @@ def test_qkv_post_rotation_norms_and_slots(H, G, d, dv, rot_dims):
     q, k, v = O.qkv_heads(proj, H=H, G=G, d=d, dv=dv, first_pos=pos0, bq=bq, bk=bk, bv=bv, freqs=freqs, eps=1e-5)
     gq, kc, vc = capi.qkv_post(proj, pos0, H, G, d, dv, bq, bk, bv, freqs, eps=1e-5, keep_first=keep, ring=ring)
     close(gq, q.reshape(T, -1), F32_TOL)
-    for t in range(T):                                             # position p sits in slot keep + (p - keep) % ring; 9 rows wrap a ring of 7
+    for t in range(T):                                             # position p sits in slot keep + (p - keep) % ring: these six run over the ring's end
         slot = keep + (pos0 + t - keep) % ring
-        if t >= T - ring:
-            close(kc[slot], k[t].reshape(-1), F32_TOL)
-            close(vc[slot], v[t].reshape(-1), F32_TOL)
+        close(kc[slot], k[t].reshape(-1), F32_TOL)
+        close(vc[slot], v[t].reshape(-1), F32_TOL)
     assert not kc[:keep].any()                                     # nobody wrote the pinned slots: these positions are past them
     # the first positions of a sequence land in the pinned slots, unrotated at position 0
     gq0, kc0, _ = capi.qkv_post(proj[:4], 0, H, G, d, dv, None, None, None, freqs, norm_qk=False, norm_v=False, keep_first=keep, ring=ring)
