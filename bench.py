@@ -429,9 +429,58 @@ def build_nabalix(z: dict, seed: int, max_tokens: int, stream):
     return m
 
 
-def run_family_workload(args):
-    """Prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes (bf16 weights, random),
-    device-timed with CUDA events on the launching stream.  One JSON line; `value` is the Nabalix decode rate at the first size."""
+def bolovik_config(z: dict) -> dict:
+    """Layers alternate: attention (window + 64 kept first positions, rotation on half of each head) with a dense feed-forward, then the gated
+    delta rule with a mixture of 16 experts of ff / 4 of which 4 are chosen (as many active feed-forward weights as the dense layer)."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
+           "mask": {"size": z["window"], "keep_first": 64},
+           "rot": {"base": 500000.0, "dims": z["head_dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    delta = {"heads": 2 * z["r_heads"], "kv_heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    pair = [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": z["ff"]}}, {"type": "delta", "mixer": delta, "mlp": moe}]
+    return {"architecture": "Bolovik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4},
+            "layers": (pair * z["layers"])[:z["layers"]]}
+
+
+def build_bolovik(z: dict, seed: int, max_tokens: int, stream):
+    """Random bf16 weights, uploaded tensor by tensor as the backend names them."""
+    import ctypes as C
+    import json
+    from xalm_b200 import capi, safetensors_io as ST, types as T
+    from xalm_b200.model import Model
+    m = Model._from_json_text(json.dumps(bolovik_config(z)), {})
+    L = capi.lib()
+    h = C.c_void_p()
+    capi.check(L.xalm_cuda_create_json(m.config["json"].encode(), 0, max_tokens, capi.PRECISION_BF16, C.byref(h)))
+    m._h = h
+    capi.check(L.xalm_cuda_set_stream(h, C.c_void_p(stream)))
+    rng = np.random.default_rng(seed)
+    for name, shape in m.expected_tensors().items():
+        leaf = name.split(".")[-1]
+        if leaf == "conv":
+            a = 0.5 * rng.standard_normal(shape, dtype=np.float32)
+        elif len(shape) == 2:
+            a = rng.standard_normal(shape, dtype=np.float32) * np.float32((2.0 if leaf == "router" else 1.0) / np.sqrt(shape[1]))
+        elif leaf == "dwa":
+            a = np.r_[np.full(shape[0] - 1, 0.1 / shape[0]), 1.0].astype(np.float32)
+        elif leaf == "A_log":
+            a = rng.uniform(-3.0, 0.0, shape).astype(np.float32)
+        elif leaf in ("b", "dt_bias"):
+            a = 0.2 * rng.standard_normal(shape, dtype=np.float32)
+        elif leaf in ("norm1", "norm2"):
+            a = 0.3 + 0.05 * rng.standard_normal(shape, dtype=np.float32)
+        else:
+            a = 1.0 + 0.1 * rng.standard_normal(shape, dtype=np.float32)
+        m.upload(name, T.BF16, shape, ST.f32_to_bf16_bits(a).view(np.uint8).reshape(-1))
+    capi.check(L.xalm_cuda_finalize(h))
+    m.config["vocab_size"] = z["vocab"]
+    return m
+
+
+def run_family_workload(args, fams=("nabalix", "llama")):
+    """Prefill and one-token-step throughput of config.json families beside one another and beside the Llama family at equal layer sizes
+    (bf16 weights, random), device-timed with CUDA events on the launching stream.  One JSON line; `value` is the first family's decode rate
+    at the first size."""
     import torch
     from xalm_b200 import capi, synth, types as T, xalm_file as X
     if not torch.cuda.is_available():
@@ -449,17 +498,17 @@ def run_family_workload(args):
             llama_full = synth.model_config("tiny", dim=z["width"], hidden_dim=z["ff"], head_dim=z["head_dim"], n_layers=z["layers"], n_heads=z["heads"],
                                             n_kv_heads=z["kv_heads"], vocab_size=z["vocab"], max_seq_len=ctx, rope_theta=10000.0, rotary_dim=z["head_dim"])
             llama_cfg = X.parse_config(synth.metadata_strings(llama_full), ctx)
-            for fam in ("nabalix", "llama"):
-                if fam == "nabalix":
+            for fam in fams:
+                if fam != "llama":
                     capi.tune("seq_chunk", args.seq_chunk)  # positions per pass of a prompt (the Llama arm takes the prompt in one pass)
-                    m = build_nabalix(z, args.seed, ctx, stream.cuda_stream)
+                    m = (build_nabalix if fam == "nabalix" else build_bolovik)(z, args.seed, ctx, stream.cuda_stream)
                 else:
                     m, _ = build_model_streaming(llama_full, llama_cfg, T.BF16, args.seed, False, stream=stream.cuda_stream)
                     capi.tune("prefill_split", 1)        # plain fp16 operands, the counterpart of the one-plane path
                 ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
                 pre = []
                 for it in range(3 + 3):                   # prompts of n_tok tokens from position 0: 3 warm-up, 3 timed
-                    if fam == "nabalix":
+                    if fam != "llama":
                         m.release()
                     flush.fill_(it)
                     ev[0].record(stream)
@@ -487,10 +536,10 @@ def run_family_workload(args):
                 m.close()
                 capi.tune("prefill_split", 3)
     first = args.sizes.split(",")[0]
-    print(json.dumps({"metric": "decode_tokens_per_s_nabalix_vs_llama", "value": rows[first]["nabalix"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
-                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": rows[first]["nabalix"]["decode_ms"], "higher_is_better": True,
+    print(json.dumps({"metric": "decode_tokens_per_s_" + "_vs_".join(fams[:2]), "value": rows[first][fams[0]]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "ms_per_step": rows[first][fams[0]]["decode_ms"], "higher_is_better": True,
                       "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                      "config": {"workload": "families", "prompt_tokens": n_tok, "sizes": {s: FAMILY_SIZES[s] for s in rows},
+                      "config": {"workload": "families" if fams[0] == "nabalix" else fams[0], "prompt_tokens": n_tok, "sizes": {s: FAMILY_SIZES[s] for s in rows},
                                  "seq_chunk": args.seq_chunk, "l2": "a 192 MB buffer is written between timed iterations", "peak_gbs": measured_peak_gbs()[0]},
                       "families": rows, "clocks": clocks.summary()}))
 
@@ -513,9 +562,11 @@ def main():
     ap.add_argument("--past-window", action="store_true",
                     help="also time steps at positions >= ctx: the KV ring is full (kv_len = ctx), 2 attention sinks active (infer.cpp:608-613)")
     ap.add_argument("--no-prefill", action="store_true", help="skip the perplexity-mode summary appended to the decode line at N=1")
-    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "perplexity", "families", "bolovik"],
                     help="decode = BASELINE config[1] (the headline metric); perplexity = config[2]: batched prefill of a 4k-token input; "
-                         "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes")
+                         "families = prefill and one-token-step throughput of the Nabalix family beside the Llama family at equal layer sizes; "
+                         "bolovik = the same for the Bolovik family beside the Nabalix and Llama families")
+    ap.add_argument("--arms", default="bolovik,nabalix,llama", help="bolovik workload: which families run, the first one is the headline")
     ap.add_argument("--seq-chunk", type=int, default=1024, help="families workload: positions per pass of a Nabalix prompt")
     ap.add_argument("--sizes", default="w1024,w2048,w4096", help="families workload: which of " + ",".join(FAMILY_SIZES))
     ap.add_argument("--tokens", type=int, default=4096, help="perplexity workload: tokens per step")
@@ -526,12 +577,12 @@ def main():
     if args.workload == "perplexity":
         run_perplexity_workload(args)
         return
-    if args.workload == "families":
+    if args.workload in ("families", "bolovik"):
         if args.steps == 256:
             args.steps = 64
         if args.tokens == 4096:
             args.tokens = 2048
-        run_family_workload(args)
+        run_family_workload(args, ("nabalix", "llama") if args.workload == "families" else tuple(args.arms.split(",")))
         return
     if args.impl == "reference":
         run_reference(args)

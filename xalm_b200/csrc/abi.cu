@@ -69,6 +69,8 @@ static std::map<std::string, int>& tuning() {
 	    {"seq_tc", 1},        // config.json families, 16-bit serving mode: passes of many tokens run their matrix products on the tcgen05 GEMM where the
 	                          // shapes allow; 1 = activations as one fp16 plane, 2 = hi + lo planes (fp32-grade), 0 = fp32 FMA kernels only
 	    {"seq_tc_min", 32},   // fewest tokens in a pass for that path
+	    {"seq_moe_tc", 1},    // config.json families with expert mixtures, 16-bit serving mode: long passes gather each expert's rows and run them on the
+	                          // tcgen05 GEMM (one small device-to-host copy of the experts' row counts per mixture layer and pass); 0 = fp32 FMA tiles
 	    {"seq_overlap", 1},   // config.json families: mixers of a layer that do not depend on one another run on two streams (two branches of the graph)
 	};
 	return t;

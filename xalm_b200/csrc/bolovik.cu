@@ -65,6 +65,7 @@ struct Layer {
 	void *w_in = nullptr, *w_o = nullptr, *w_gu = nullptr, *w_down = nullptr, *w_router = nullptr;
 	WMat m_in, m_o, m_gu, m_down;
 	TcWeight t_in, t_o, t_gu, t_down;
+	std::vector<TcWeight> t_egu, t_edown; // per expert, when the mixture's long passes run on the tensor cores
 	float *norm1 = nullptr, *norm2 = nullptr, *dwa = nullptr;
 };
 
@@ -80,6 +81,8 @@ struct BolovikModel : SeqModel {
 	int part_cap = 0;
 	int *moe_idx = nullptr, *moe_sorted = nullptr, *moe_tiles = nullptr, *moe_ntiles = nullptr;
 	float *moe_wgt = nullptr, *moe_hid = nullptr, *moe_out = nullptr;
+	int *moe_off = nullptr, *moe_inv = nullptr, *h_off = nullptr; // first place of every expert in the sorted pairs (device, pinned host), inverse order
+	float* moe_x = nullptr;                                        // the pairs' input rows in sorted order
 };
 typedef BolovikModel Bv;
 
@@ -225,11 +228,11 @@ int parse_config(SeqModel* sm, const char* json) {
 
 // ---- the kernels of one pass ----------------------------------------------------------------------------------------------------------
 // x + gnorm(y) for one sublayer; with `last` the layer's result lands in hist[li + 1] and the depth average (if the layer has one) in xavg
-int enqueue_norm_add(Bv* m, size_t li, const Layer& L, bool second, bool last, const float* x_in, const float* y, int ldy, int parts, const float* part_w, int n,
-                     int* nl) {
+int enqueue_norm_add(Bv* m, size_t li, const Layer& L, bool second, bool last, const float* x_in, const float* y, int ldy, int parts, const float* part_w,
+                     const int* part_row, int n, int* nl) {
 	const size_t hs = (size_t) m->chunk * m->width;
 	GroupNormArgs g;
-	g.y = y; g.ldy = ldy; g.parts = parts; g.part_w = part_w;
+	g.y = y; g.ldy = ldy; g.parts = parts; g.part_w = part_w; g.part_row = part_row;
 	g.w = second ? L.norm2 : L.norm1;
 	g.groups = m->groups; g.width = m->width; g.eps = m->eps;
 	g.x_in = x_in;
@@ -297,7 +300,7 @@ int enqueue_pass(SeqModel* sm, int n, int want, int* nl) {
 		}
 		est.out = m->y; est.ldo = W;
 		XALM_TRY(rows_product(m, m->att, H * dv, L.w_o, &L.t_o, n, W, H * dv, est, nl));
-		XALM_TRY(enqueue_norm_add(m, li, L, false, L.ff_kind == FF_NONE, x, m->y, W, 1, nullptr, n, nl));
+		XALM_TRY(enqueue_norm_add(m, li, L, false, L.ff_kind == FF_NONE, x, m->y, W, 1, nullptr, nullptr, n, nl));
 		const float* x1 = m->hist + (li + 1) * hs;
 		if (L.ff_kind == FF_DENSE) {
 			RowsEpi eg;
@@ -305,26 +308,53 @@ int enqueue_pass(SeqModel* sm, int n, int want, int* nl) {
 			XALM_TRY(rows_product(m, x1, W, L.w_gu, &L.t_gu, n, 2 * L.ff, W, eg, nl));
 			est.out = m->y; est.ldo = W;
 			XALM_TRY(rows_product(m, m->ffh, L.ff, L.w_down, &L.t_down, n, W, L.ff, est, nl));
-			XALM_TRY(enqueue_norm_add(m, li, L, true, true, x1, m->y, W, 1, nullptr, n, nl));
+			XALM_TRY(enqueue_norm_add(m, li, L, true, true, x1, m->y, W, 1, nullptr, nullptr, n, nl));
 		} else if (L.ff_kind == FF_MOE) {
 			MoeRouteArgs ra = {};
 			ra.h = x1; ra.ldh = W; ra.w = L.w_router; ra.w_bf16 = m->w_bf16;
 			ra.E = L.E; ra.top = L.top; ra.K = W; ra.n_groups = L.n_groups; ra.keep_groups = L.keep_groups;
 			ra.idx = m->moe_idx; ra.wgt = m->moe_wgt; ra.step = m->d_step;
 			XALM_TRY(launch_moe_router(ra, n, s));
-			MoeSortArgs so = {m->moe_idx, L.top, L.E, m->d_step, m->moe_sorted, m->moe_tiles, m->moe_ntiles};
-			XALM_TRY(launch_moe_sort(so, s));
-			MoeGemmArgs ga = {};
-			ga.A = x1; ga.lda = W; ga.a_div = L.top; ga.W = L.w_gu; ga.N = 2 * L.ff; ga.K = W;
-			ga.sorted = m->moe_sorted; ga.tiles = m->moe_tiles; ga.n_tiles = m->moe_ntiles;
-			ga.e.kind = EPI_GLU; ga.e.glu_act = GLU_SILU; ga.e.out = m->moe_hid; ga.e.ldo = L.ff;
-			XALM_TRY(launch_moe_gemm(ga, m->w_bf16, n * L.top, L.E, s));
-			ga.A = m->moe_hid; ga.lda = L.ff; ga.a_div = 1; ga.W = L.w_down; ga.N = W; ga.K = L.ff;
-			ga.e = RowsEpi();
-			ga.e.kind = EPI_STORE; ga.e.out = m->moe_out; ga.e.ldo = W;
-			XALM_TRY(launch_moe_gemm(ga, m->w_bf16, n * L.top, L.E, s));
-			*nl += 4;
-			XALM_TRY(enqueue_norm_add(m, li, L, true, true, x1, m->moe_out, W, L.top, m->moe_wgt, n, nl));
+			const bool on_tc = m->use_tc && !L.t_egu.empty() && n >= m->tc_min_rows;
+			const bool tiled = on_tc || n * L.top > MOE_MATVEC_PAIRS; // steps of a few tokens run one matvec per (token, slot) pair and need no tile list
+			if (tiled) {
+				MoeSortArgs so = {m->moe_idx, L.top, L.E, m->d_step, m->moe_sorted, m->moe_tiles, m->moe_ntiles, m->moe_off, m->moe_inv};
+				XALM_TRY(launch_moe_sort(so, s));
+				(*nl)++;
+			}
+			(*nl)++;
+			if (on_tc) {
+				// Long passes of the 16-bit mode: each expert's rows, gathered one after the other, go through the tcgen05 GEMM on that expert's
+				// resident fp16 tiles.  How many rows each expert got is read back first (one small copy and a wait per mixture layer and pass).
+				XALM_CUDA_CHECK(cudaMemcpyAsync(m->h_off, m->moe_off, (size_t) (L.E + 1) * 4, cudaMemcpyDeviceToHost, s));
+				moe_gather_kernel<<<n * L.top, 256, 0, s>>>(x1, W, L.top, m->moe_sorted, m->d_step, L.top, W, m->moe_x);
+				XALM_SEQ_LAUNCH_CHECK("moe_gather");
+				XALM_CUDA_CHECK(cudaStreamSynchronize(s));
+				RowsEpi eg;
+				eg.kind = EPI_GLU; eg.glu_act = GLU_SILU; eg.ldo = L.ff;
+				for (int e = 0; e < L.E; e++) {
+					const int at = m->h_off[e], cnt = m->h_off[e + 1] - at;
+					if (cnt <= 0) continue;
+					XALM_TRY(tc_gemm(L.t_egu[(size_t) e], m->moe_x + (size_t) at * W, cnt, m->tc_out, 2 * L.ff, m->a_hi, m->a_lo, s));
+					eg.out = m->moe_hid + (size_t) at * L.ff;
+					XALM_TRY(launch_rows_epilogue(m->tc_out, 2 * L.ff, cnt, 2 * L.ff, eg, s));
+					XALM_TRY(tc_gemm(L.t_edown[(size_t) e], m->moe_hid + (size_t) at * L.ff, cnt, m->moe_out + (size_t) at * W, W, m->a_hi, m->a_lo, s));
+					*nl += 5;
+				}
+			} else {
+				MoeGemmArgs ga = {};
+				ga.A = x1; ga.lda = W; ga.a_div = L.top; ga.W = L.w_gu; ga.N = 2 * L.ff; ga.K = W;
+				ga.sorted = m->moe_sorted; ga.tiles = m->moe_tiles; ga.n_tiles = m->moe_ntiles;
+				ga.idx = m->moe_idx; ga.step = m->d_step; ga.top = L.top;
+				ga.e.kind = EPI_GLU; ga.e.glu_act = GLU_SILU; ga.e.out = m->moe_hid; ga.e.ldo = L.ff;
+				XALM_TRY(launch_moe_gemm(ga, m->w_bf16, n * L.top, L.E, s));
+				ga.A = m->moe_hid; ga.lda = L.ff; ga.a_div = 1; ga.W = L.w_down; ga.N = W; ga.K = L.ff;
+				ga.e = RowsEpi();
+				ga.e.kind = EPI_STORE; ga.e.out = m->moe_out; ga.e.ldo = W;
+				XALM_TRY(launch_moe_gemm(ga, m->w_bf16, n * L.top, L.E, s));
+				*nl += 2;
+			}
+			XALM_TRY(enqueue_norm_add(m, li, L, true, true, x1, m->moe_out, W, L.top, m->moe_wgt, on_tc ? m->moe_inv : nullptr, n, nl));
 		}
 		x = L.dwa ? m->xavg : x1;
 	}
@@ -351,6 +381,7 @@ int finalize(SeqModel* sm) {
 	auto T = [&](const std::string& n) { return tensor_or_null(m, n); };
 	size_t max_in = 4, max_prep = 4, max_att = 1, max_ff = 1, max_hdv = 1, max_h = 1, max_pairs = 0, max_moe_hid = 0;
 	int max_tiles = 1;
+	bool moe_tc = false;
 	const size_t kelem = m->precision == XALM_PRECISION_F32 ? 4 : 2;
 	for (size_t li = 0; li < m->layers.size(); li++) {
 		Layer& L = m->layers[li];
@@ -408,8 +439,8 @@ int finalize(SeqModel* sm) {
 				gu.push_back(T(pe + "up"));
 				dn.push_back(T(pe + "down"));
 			}
-			XALM_TRY(upload_rows(m, gu, W, true, &L.w_gu, nullptr));
-			XALM_TRY(upload_rows(m, dn, L.ff, false, &L.w_down, nullptr));
+			XALM_TRY(upload_rows(m, gu, W, true, &L.w_gu, &L.m_gu));   // all experts, one after the other
+			XALM_TRY(upload_rows(m, dn, L.ff, false, &L.w_down, &L.m_down));
 			XALM_TRY(upload_rows(m, {T(p + "mlp.router")}, W, false, &L.w_router, nullptr));
 			XALM_TRY(moe_prepare(W, L.E, L.n_groups));
 			max_pairs = std::max(max_pairs, C * L.top);
@@ -424,6 +455,21 @@ int finalize(SeqModel* sm) {
 		if (L.ff_kind == FF_DENSE) {
 			XALM_TRY(tc_register(m, L.m_gu, &L.t_gu));
 			XALM_TRY(tc_register(m, L.m_down, &L.t_down));
+		}
+		// a mixture whose expert shapes the GEMM takes keeps fp16 tiles per expert for its long passes
+		if (L.ff_kind == FF_MOE && m->use_tc && tune("seq_moe_tc") && tc_shape_ok(2 * L.ff, W, 2 * L.ff) && tc_shape_ok(W, L.ff, W)) {
+			L.t_egu.resize((size_t) L.E);
+			L.t_edown.resize((size_t) L.E);
+			for (int e = 0; e < L.E; e++) {
+				WMat gu = L.m_gu, dn = L.m_down; // this expert's rows of the stacked matrices
+				gu.rows = 2 * L.ff;
+				gu.p0 = static_cast<const uint8_t*>(L.m_gu.p0) + (size_t) e * 2 * L.ff * L.m_gu.s0;
+				dn.rows = W;
+				dn.p0 = static_cast<const uint8_t*>(L.m_down.p0) + (size_t) e * W * L.m_down.s0;
+				XALM_TRY(tc_register(m, gu, &L.t_egu[(size_t) e]));
+				XALM_TRY(tc_register(m, dn, &L.t_edown[(size_t) e]));
+			}
+			moe_tc = true;
 		}
 	}
 	m->proj_ld = (int) ((max_in + 3) / 4 * 4);
@@ -448,6 +494,14 @@ int finalize(SeqModel* sm) {
 		XALM_TRY(dev_alloc(m, &m->moe_ntiles, 1, true));
 		XALM_TRY(dev_alloc(m, &m->moe_hid, max_moe_hid));
 		XALM_TRY(dev_alloc(m, &m->moe_out, max_pairs * W));
+		if (moe_tc) {
+			int max_e = 1;
+			for (const Layer& L : m->layers) max_e = std::max(max_e, L.E);
+			XALM_TRY(dev_alloc(m, &m->moe_off, (size_t) max_e + 1, true));
+			XALM_TRY(dev_alloc(m, &m->moe_inv, max_pairs, true));
+			XALM_TRY(dev_alloc(m, &m->moe_x, max_pairs * W));
+			XALM_CUDA_CHECK(cudaMallocHost(&m->h_off, ((size_t) max_e + 1) * 4));
+		}
 	}
 	return XALM_OK;
 }
@@ -489,7 +543,12 @@ bool state_buffer(SeqModel* sm, int layer, const float** src, size_t* count) {
 void destroy(SeqModel* sm) {
 	Bv* m = static_cast<Bv*>(sm);
 	for (Layer& L : m->layers)
+	{
 		for (TcWeight* t : {&L.t_in, &L.t_o, &L.t_gu, &L.t_down}) tc_weight_free(t);
+		for (TcWeight& t : L.t_egu) tc_weight_free(&t);
+		for (TcWeight& t : L.t_edown) tc_weight_free(&t);
+	}
+	if (m->h_off) cudaFreeHost(m->h_off);
 	delete m;
 }
 

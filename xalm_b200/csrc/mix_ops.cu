@@ -340,10 +340,11 @@ int xalm_cuda_moe_ffn(float* out_pairs, int* idx, float* wgt, const float* h, co
 	ra.h = pool.put(h, (size_t) T * K); ra.ldh = K; ra.w = put_w(w_router, (size_t) E * K); ra.w_bf16 = w_bf16;
 	ra.E = E; ra.top = top; ra.K = K; ra.n_groups = n_groups; ra.keep_groups = keep_groups;
 	ra.idx = pool.raw<int>((size_t) P); ra.wgt = pool.raw<float>((size_t) P); ra.step = d_st;
-	MoeSortArgs so = {ra.idx, top, E, d_st, pool.raw<int>((size_t) P), pool.raw<int>((size_t) 3 * max_tiles), pool.raw<int>(1)};
+	MoeSortArgs so = {ra.idx, top, E, d_st, pool.raw<int>((size_t) P), pool.raw<int>((size_t) 3 * max_tiles), pool.raw<int>(1), nullptr, nullptr};
 	MoeGemmArgs ga = {};
 	ga.A = ra.h; ga.lda = K; ga.a_div = top; ga.W = put_w(gu.data(), gu.size()); ga.N = 2 * ff; ga.K = K;
 	ga.sorted = so.sorted; ga.tiles = so.tiles; ga.n_tiles = so.n_tiles;
+	ga.idx = ra.idx; ga.step = d_st; ga.top = top;
 	float* hid = pool.raw<float>((size_t) P * ff);
 	float* outp = pool.raw<float>((size_t) P * K);
 	ga.e.kind = EPI_GLU; ga.e.glu_act = act; ga.e.out = hid; ga.e.ldo = ff; ga.e.limit = INFINITY;

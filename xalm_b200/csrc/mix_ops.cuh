@@ -1397,6 +1397,7 @@ struct GroupNormArgs {
 	const float* y = nullptr;      // (rows * parts, ldy)
 	int ldy = 0, parts = 1;
 	const float* part_w = nullptr; // (rows, parts), or NULL: parts == 1 with weight 1
+	const int* part_row = nullptr; // (rows, parts) row of y that holds part k of token t, or NULL: t * parts + k
 	const float* w = nullptr;      // (width)
 	int groups = 1, width = 0;
 	float eps = 1e-5f;
@@ -1415,13 +1416,26 @@ static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
 	float* rinv = sm + a.width;  // groups
 	const int t = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
 	const int W = a.width, gs = W / a.groups;
-	for (int c = tid; c < W; c += nth) {
-		float v;
-		if (a.part_w) {
-			v = 0.f;
-			for (int k = 0; k < a.parts; k++) v = fmaf(a.part_w[(size_t) t * a.parts + k], a.y[((size_t) t * a.parts + k) * a.ldy + c], v);
-		} else v = a.y[(size_t) t * a.ldy + c];
-		u[c] = v;
+	// four columns per thread at a time, every load of the four issued before the first use: a one-token step runs one CTA of this kernel,
+	// and its time is the number of dependent trips to memory
+	for (int c0 = tid; c0 < W; c0 += 4 * nth) {
+		float v[4];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth;
+			v[k] = 0.f;
+			if (c < W) {
+				if (a.part_w) {
+					for (int p = 0; p < a.parts; p++) {
+						const size_t pk = (size_t) t * a.parts + p;
+						v[k] = fmaf(a.part_w[pk], a.y[(a.part_row ? (size_t) a.part_row[pk] : pk) * a.ldy + c], v[k]);
+					}
+				} else v[k] = a.y[(size_t) t * a.ldy + c];
+			}
+		}
+#pragma unroll
+		for (int k = 0; k < 4; k++)
+			if (c0 + k * nth < W) u[c0 + k * nth] = v[k];
 	}
 	__syncthreads();
 	for (int g = warp; g < a.groups; g += nw) {
@@ -1431,18 +1445,39 @@ static __global__ void group_norm_residual_kernel(GroupNormArgs a) {
 		if (lane == 0) rinv[g] = 1.f / sqrtf(ss / (float) gs + a.eps);
 	}
 	__syncthreads();
-	for (int c = tid; c < W; c += nth) {
-		const size_t at = (size_t) t * W + c;
-		float v = u[c] * rinv[c / gs] * a.w[c];
-		if (a.x_in) v += a.x_in[at];
-		a.x_out[at] = v;
-		if (a.dwa) {
-			float s = 0.f;
-			for (int j = 0; j < a.n_hist; j++) s = fmaf(a.dwa[j], a.hist[(size_t) j * a.hist_stride + at], s);
-			v = fmaf(a.dwa[a.n_hist], v, s);
-			a.avg_out[at] = v;
+	for (int c0 = tid; c0 < W; c0 += 4 * nth) {
+		float wv[4], xi[4], acc[4];
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth;
+			const bool in = c < W;
+			wv[k] = in ? a.w[c] : 0.f;
+			xi[k] = (in && a.x_in) ? a.x_in[(size_t) t * W + c] : 0.f;
+			acc[k] = 0.f;
 		}
-		if (a.keep_out) a.keep_out[at] = v;
+		if (a.dwa)
+			for (int j = 0; j < a.n_hist; j++) {
+				const float cj = a.dwa[j];
+				float hv[4];
+#pragma unroll
+				for (int k = 0; k < 4; k++) hv[k] = c0 + k * nth < W ? a.hist[(size_t) j * a.hist_stride + (size_t) t * W + c0 + k * nth] : 0.f;
+#pragma unroll
+				for (int k = 0; k < 4; k++) acc[k] = fmaf(cj, hv[k], acc[k]);
+			}
+#pragma unroll
+		for (int k = 0; k < 4; k++) {
+			const int c = c0 + k * nth;
+			if (c >= W) continue;
+			const size_t at = (size_t) t * W + c;
+			float v = u[c] * rinv[c / gs] * wv[k];
+			if (a.x_in) v += xi[k];
+			a.x_out[at] = v;
+			if (a.dwa) {
+				v = fmaf(a.dwa[a.n_hist], v, acc[k]);
+				a.avg_out[at] = v;
+			}
+			if (a.keep_out) a.keep_out[at] = v;
+		}
 	}
 }
 static inline size_t group_norm_smem(int width, int groups) { return (size_t) (width + groups) * 4; }

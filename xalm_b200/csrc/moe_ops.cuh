@@ -56,7 +56,16 @@ __global__ void __launch_bounds__(256) moe_router_kernel(MoeRouteArgs a) {
 	const WT* W = reinterpret_cast<const WT*>(a.w);
 	for (int e = warp; e < a.E; e += nw) {
 		float z = 0.f;
-		for (int k = lane; k < a.K; k += 32) z = fmaf(ldf(W + (size_t) e * a.K + k), hs[k], z);
+		if ((a.K & 7) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 31) == 0) {
+#pragma unroll 4
+			for (int k = lane * 8; k < a.K; k += 256) {
+				float wv[8];
+				ld8(W + (size_t) e * a.K + k, wv);
+#pragma unroll
+				for (int i = 0; i < 8; i++) z = fmaf(wv[i], hs[k + i], z);
+			}
+		} else
+			for (int k = lane; k < a.K; k += 32) z = fmaf(ldf(W + (size_t) e * a.K + k), hs[k], z);
 		z = warp_sum(z);
 		if (lane == 0) sc[e] = sigmoidf_(z);
 	}
@@ -114,6 +123,8 @@ struct MoeSortArgs {
 	int* sorted;  // (T * top) pair ids, expert after expert
 	int* tiles;   // (max_tiles, 3): expert, first place in `sorted`, rows
 	int* n_tiles; // (1)
+	int* off;     // (E + 1) first place of every expert in `sorted`, or NULL
+	int* inv;     // (T * top) place of every pair in `sorted`, or NULL
 };
 // one CTA; shared memory: 2 E + 1 ints
 static __global__ void moe_sort_kernel(MoeSortArgs a) {
@@ -137,12 +148,29 @@ static __global__ void moe_sort_kernel(MoeSortArgs a) {
 			}
 			at += cnt[e];
 		}
+		off[a.E] = at;
 		*a.n_tiles = nt;
 	}
 	__syncthreads();
 	for (int e = tid; e < a.E; e += nth) cnt[e] = off[e]; // cursors
 	__syncthreads();
-	for (int p = tid; p < P; p += nth) a.sorted[atomicAdd(&cnt[a.idx[p]], 1)] = p; // the order inside an expert does not matter: rows are independent
+	for (int p = tid; p < P; p += nth) { // the order inside an expert does not matter: rows are independent
+		const int place = atomicAdd(&cnt[a.idx[p]], 1);
+		a.sorted[place] = p;
+		if (a.inv) a.inv[p] = place;
+	}
+	if (a.off)
+		for (int e = tid; e <= a.E; e += nth) a.off[e] = off[e];
+}
+
+// rows of the pairs in sorted order, one after the other: dst[place] = src[sorted[place] / div] (the tensor-core products want each expert's rows
+// contiguous)
+static __global__ void moe_gather_kernel(const float* __restrict__ src, int lds, int div, const int* __restrict__ sorted, const SeqStep* step, int top, int width,
+                                         float* __restrict__ dst) {
+	const int place = blockIdx.x;
+	if (place >= step->n * top) return;
+	const float* row = src + (size_t) (sorted[place] / div) * lds;
+	for (int c = threadIdx.x; c < width; c += blockDim.x) dst[(size_t) place * width + c] = row[c];
 }
 
 struct MoeGemmArgs {
@@ -154,6 +182,10 @@ struct MoeGemmArgs {
 	const int* tiles;
 	const int* n_tiles;
 	RowsEpi e;      // rows of the output are pair ids
+	// steps of a few tokens skip the tile list: one matvec per (token, slot) pair
+	const int* idx; // (T, top) the pairs' experts
+	const SeqStep* step;
+	int top;
 };
 
 // 64 x 64 x 16 tiles, 4 x 4 per thread, as rows_gemm_kernel; blockIdx.y walks the tile list
@@ -211,6 +243,63 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(MoeGemmArgs a) {
 	}
 }
 
+// ---- the same for steps of a few tokens: every (token, slot) pair is a matvec of its own expert (blockIdx.y = pair), a warp per pair of
+// output columns, or KS warps of the CTA per pair of columns (each a slice of K) when there are too few columns to fill the machine ------
+template <typename WT, int KS>
+__global__ void __launch_bounds__(256) moe_matvec_kernel(MoeGemmArgs a) {
+	__shared__ float red[8][2];
+	const int p = blockIdx.y;
+	if (p >= a.step->n * a.top) return;
+	const int N = a.N, K = a.K;
+	const WT* W = reinterpret_cast<const WT*>(a.W) + (size_t) a.idx[p] * N * K;
+	const float* A = a.A + (size_t) (p / a.a_div) * a.lda;
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, ks = warp % KS;
+	const int c0 = (blockIdx.x * (8 / KS) + warp / KS) * 2;
+	const bool live = c0 < N, two = c0 + 1 < N;
+	float acc0 = 0.f, acc1 = 0.f;
+	if (live) {
+		const WT* w0 = W + (size_t) c0 * K;
+		const WT* w1 = W + (size_t) (two ? c0 + 1 : c0) * K;
+		const bool vec = (K % 8 == 0) && (a.lda % 4 == 0) && ((reinterpret_cast<uintptr_t>(a.W) & 31) == 0) && ((reinterpret_cast<uintptr_t>(a.A) & 15) == 0);
+		if (vec) {
+#pragma unroll 2
+			for (int k = (ks * 32 + lane) * 8; k < K; k += 256 * KS) {
+				float a0[8], a1[8], x[8];
+				ld8(w0 + k, a0);
+				ld8(w1 + k, a1);
+				ld8(A + k, x);
+#pragma unroll
+				for (int i = 0; i < 8; i++) {
+					acc0 = fmaf(a0[i], x[i], acc0);
+					acc1 = fmaf(a1[i], x[i], acc1);
+				}
+			}
+		} else {
+			for (int k = ks * 32 + lane; k < K; k += 32 * KS) {
+				const float x = A[k];
+				acc0 = fmaf(ldf(w0 + k), x, acc0);
+				acc1 = fmaf(ldf(w1 + k), x, acc1);
+			}
+		}
+		acc0 = warp_sum(acc0);
+		acc1 = warp_sum(acc1);
+	}
+	if (KS > 1) {
+		if (lane == 0) { red[warp][0] = acc0; red[warp][1] = acc1; }
+		__syncthreads();
+		if (ks == 0 && lane == 0)
+			for (int j = 1; j < KS; j++) { acc0 += red[warp + j][0]; acc1 += red[warp + j][1]; }
+	}
+	if (live && ks == 0 && lane == 0) {
+		if (a.e.kind == EPI_GLU) {
+			if (two) epi_apply(a.e, p, c0, N, acc0, acc1);
+		} else {
+			epi_apply(a.e, p, c0, N, acc0, 0.f);
+			if (two) epi_apply(a.e, p, c0 + 1, N, acc1, 0.f);
+		}
+	}
+}
+
 // ---- launchers ------------------------------------------------------------------------------------------------------------------
 static inline size_t moe_router_smem(int K, int E, int n_groups) { return (size_t) (K + 2 * E + std::max(n_groups, 1)) * 4; }
 static inline int moe_prepare(int K, int E, int n_groups) { // outside a stream capture
@@ -235,7 +324,25 @@ static inline int launch_moe_sort(const MoeSortArgs& a, cudaStream_t s) {
 	return launch_check("moe_sort");
 }
 // pairs: host-side bound of the step's (token, slot) pairs
+constexpr int MOE_MATVEC_PAIRS = 32; // up to this many pairs in a step, each pair is a matvec of its own
 static inline int launch_moe_gemm(const MoeGemmArgs& a, bool w_bf16, int pairs, int E, cudaStream_t s) {
+	if (pairs <= MOE_MATVEC_PAIRS && a.idx && a.step) {
+		const int cols = (a.N + 1) / 2;
+		int ks = 1; // warps per column pair: enough CTAs for two per SM, each slice of K at least 256 long
+		while (ks < 8 && (long long) ((cols * ks + 7) / 8) * pairs < 296 && a.K >= 512 * ks) ks *= 2;
+		const dim3 grid((cols * ks + 7) / 8, pairs);
+#define XALM_MOE_MATVEC(WT_)                                                             \
+	do {                                                                                 \
+		if (ks == 1) moe_matvec_kernel<WT_, 1><<<grid, 256, 0, s>>>(a);                  \
+		else if (ks == 2) moe_matvec_kernel<WT_, 2><<<grid, 256, 0, s>>>(a);             \
+		else if (ks == 4) moe_matvec_kernel<WT_, 4><<<grid, 256, 0, s>>>(a);             \
+		else moe_matvec_kernel<WT_, 8><<<grid, 256, 0, s>>>(a);                          \
+	} while (0)
+		if (w_bf16) XALM_MOE_MATVEC(__nv_bfloat16);
+		else XALM_MOE_MATVEC(float);
+#undef XALM_MOE_MATVEC
+		return launch_check("moe_matvec");
+	}
 	const dim3 grid((a.N + 63) / 64, moe_max_tiles(pairs, E));
 	if (w_bf16) moe_gemm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(a);
 	else moe_gemm_kernel<float><<<grid, 256, 0, s>>>(a);
