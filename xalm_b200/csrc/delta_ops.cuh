@@ -102,18 +102,24 @@ constexpr int DELTA_TT = 16; // tokens staged at a time
 
 // A column of the state is shared by NS neighbouring lanes, each keeping DS of its d values in registers (d <= DS * NS); the two dot
 // products of a token are completed with log2(NS) shuffles.  DS == 0: one thread per column, the state in shared memory (any d that fits).
+// one 4-byte element, global -> shared, without a register in between: every copy of a tile is in flight at once
+__device__ __forceinline__ void delta_cp4(float* dst, const float* src) {
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned) __cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
 template <int DS, int NS>
 __global__ void __launch_bounds__(512) delta_rule_kernel(DeltaArgs a) {
 	extern __shared__ __align__(16) float sm[];
 	const int h = blockIdx.x, tid = threadIdx.x, nth = blockDim.x, lane = tid & 31, warp = tid >> 5, nw = nth >> 5;
 	const int d = a.d, dv = a.dv, dp = DS > 0 ? DS * NS : ((d + 3) & ~3), hk = h / (a.H / a.G);
 	const int nq = a.G * d, Cc = 2 * nq + a.H * dv;
-	float* ks = sm;                         // TT * dp
-	float* qs = ks + DELTA_TT * dp;         // TT * dp
-	float* vs = qs + DELTA_TT * dp;         // TT * dv
-	float* och = vs + DELTA_TT * dv;        // TT * dv
-	float* bg = och + DELTA_TT * dv;        // TT * 2: beta, g
-	float* Ssh = bg + DELTA_TT * 2;         // DS == 0: dp * nth
+	// a token's k (and q) in shared memory: the NS slices 4 floats apart from one another's end, so that the 16-byte reads of a warp's NS
+	// slices fall on different banks
+	const int dps = DS > 0 ? NS * (DS + 4) : dp;
+	// two tile buffers (the next tile's copies fly while this one is scanned): k | q | v | gate | beta, g
+	const int tile_floats = DELTA_TT * (2 * dps + 2 * dv + 2);
+	float* och = sm + 2 * tile_floats;      // TT * dv
+	float* Ssh = och + DELTA_TT * dv;       // DS == 0: dp * nth
 	const int T = a.step->n;
 	const int c = tid / NS, sl = tid % NS, i0 = sl * DS; // this thread's column and its slice of d
 	const bool live = c < dv;
@@ -125,30 +131,45 @@ __global__ void __launch_bounds__(512) delta_rule_kernel(DeltaArgs a) {
 	} else {
 		for (int i = 0; i < dp; i++) Ssh[(size_t) i * nth + tid] = (live && i < d) ? st[(size_t) i * dv + c] : 0.f;
 	}
-	for (int t0 = 0; t0 < T; t0 += DELTA_TT) {
+	if (dp != d) { // channels beyond d that the scan reads stay zero: copies touch real channels only
+		for (int x = tid; x < 2 * tile_floats; x += nth) sm[x] = 0.f;
+		__syncthreads();
+	}
+	auto stage = [&](float* buf, int t0) {
 		const int nt = min(DELTA_TT, T - t0);
-		__syncthreads(); // the last tile's readers are done
-		for (int x = tid; x < nt * dp; x += nth) {
-			const int tt = x / dp, i = x % dp;
+		float *ks = buf, *qs = ks + DELTA_TT * dps, *vs = qs + DELTA_TT * dps, *gs = vs + DELTA_TT * dv, *bg = gs + DELTA_TT * dv;
+		for (int x = tid; x < nt * d; x += nth) {
+			const int tt = x / d, i = x % d;
 			const float* prow = a.prep + (size_t) (t0 + tt) * a.ldp;
-			ks[x] = i < d ? prow[nq + hk * d + i] : 0.f;
-			qs[x] = i < d ? prow[hk * d + i] : 0.f;
+			const int at = tt * dps + (DS > 0 ? (i / (DS > 0 ? DS : 1)) * (DS + 4) + i % (DS > 0 ? DS : 1) : i);
+			delta_cp4(ks + at, prow + nq + hk * d + i);
+			delta_cp4(qs + at, prow + hk * d + i);
 		}
 		for (int x = tid; x < nt * dv; x += nth) {
 			const int tt = x / dv, cc = x % dv;
-			vs[x] = a.prep[(size_t) (t0 + tt) * a.ldp + 2 * nq + h * dv + cc];
+			delta_cp4(vs + x, a.prep + (size_t) (t0 + tt) * a.ldp + 2 * nq + h * dv + cc);
+			delta_cp4(gs + x, a.proj + (size_t) (t0 + tt) * a.ld + a.g_off + h * dv + cc);
 		}
-		for (int x = tid; x < nt * 2; x += nth) {
-			const int tt = x >> 1, w = x & 1;
-			bg[x] = a.prep[(size_t) (t0 + tt) * a.ldp + Cc + w * a.H + h];
-		}
+		for (int x = tid; x < nt * 2; x += nth) delta_cp4(bg + x, a.prep + (size_t) (t0 + (x >> 1)) * a.ldp + Cc + (x & 1) * a.H + h);
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	if (T > 0) stage(sm, 0);
+	int cur = 0;
+	for (int t0 = 0; t0 < T; t0 += DELTA_TT, cur ^= 1) {
+		const int nt = min(DELTA_TT, T - t0);
+		const float *ks = sm + cur * tile_floats, *qs = ks + DELTA_TT * dps, *vs = qs + DELTA_TT * dps, *gs = vs + DELTA_TT * dv, *bg = gs + DELTA_TT * dv;
+		__syncthreads(); // the other buffer's last readers (the tile before this one) are done
+		if (t0 + DELTA_TT < T) {
+			stage(sm + (cur ^ 1) * tile_floats, t0 + DELTA_TT);
+			asm volatile("cp.async.wait_group 1;" ::: "memory");
+		} else asm volatile("cp.async.wait_group 0;" ::: "memory");
 		__syncthreads();
 		for (int tt = 0; tt < nt; tt++) { // every lane takes part (the shuffles want whole warps); dead columns compute on zeros
 			const float beta = bg[2 * tt], g = bg[2 * tt + 1], v = live ? vs[tt * dv + c] : 0.f;
 			float o;
 			if constexpr (DS > 0) {
-				const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dp + i0);
-				const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dp + i0);
+				const float4* k4 = reinterpret_cast<const float4*>(ks + tt * dps + sl * (DS + 4));
+				const float4* q4 = reinterpret_cast<const float4*>(qs + tt * dps + sl * (DS + 4));
 				float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
 				for (int i = 0; i < DS; i += 4) {
@@ -201,10 +222,9 @@ __global__ void __launch_bounds__(512) delta_rule_kernel(DeltaArgs a) {
 				ss = warp_sum(ss);
 				r = 1.f / sqrtf(ss / (float) dv + a.eps);
 			}
-			const float* grow = a.proj + (size_t) (t0 + tt) * a.ld + a.g_off + h * dv;
 			float* orow = a.out + (size_t) (t0 + tt) * (a.H * dv) + h * dv;
 			for (int cc = lane; cc < dv; cc += 32) {
-				const float z = grow[cc];
+				const float z = gs[tt * dv + cc];
 				orow[cc] = och[tt * dv + cc] * r * (a.norm_w ? a.norm_w[cc] : 1.f) * (z * sigmoidf_(z));
 			}
 		}
@@ -242,8 +262,8 @@ static inline DeltaShape delta_shape(int d, int dv) {
 }
 static inline size_t delta_rule_smem(int d, int dv) {
 	const DeltaShape z = delta_shape(d, dv);
-	const int dp = z.DS ? z.DS * z.NS : ((d + 3) & ~3);
-	return sizeof(float) * ((size_t) DELTA_TT * (2 * dp + 2 * dv + 2) + (z.DS ? 0 : (size_t) dp * z.threads));
+	const int dp = z.DS ? z.NS * (z.DS + 4) : ((d + 3) & ~3);
+	return sizeof(float) * (2 * (size_t) DELTA_TT * (2 * dp + 2 * dv + 2) + (size_t) DELTA_TT * dv + (z.DS ? 0 : (size_t) dp * z.threads));
 }
 static inline bool delta_ok(int d, int dv) { return dv <= 512 && delta_rule_smem(d, dv) <= 200 * 1024; }
 #define XALM_DELTA_DISPATCH(z_, CALL)                                      \
