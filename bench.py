@@ -434,11 +434,11 @@ def bolovik_config(z: dict) -> dict:
     delta rule with a mixture of 16 experts of ff / 4 of which 4 are chosen (as many active feed-forward weights as the dense layer)."""
     att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"], "scale": z["head_dim"] ** -0.5,
            "mask": {"size": z["window"], "keep_first": 64},
-           "rot": {"base": 500000.0, "dims": z["head_dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+           "rot": {"base": 10000.0, "dims": z["head_dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     delta = {"heads": 2 * z["r_heads"], "kv_heads": z["r_heads"], "dim": z["r_dim"], "vdim": z["r_vdim"], "conv": 4}
     moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
     pair = [{"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": z["ff"]}}, {"type": "delta", "mixer": delta, "mlp": moe}]
-    return {"architecture": "Bolovik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5, "groups": 4},
+    return {"architecture": "Bolovik", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6, "groups": 8},
             "layers": (pair * z["layers"])[:z["layers"]]}
 
 

@@ -114,7 +114,7 @@ void xalm_cuda_destroy(xalm_cuda_model* m);
  *               XALM_PRECISION_F32  = everything in IEEE fp32 (no TF32), the K/V cache included. */
 enum xalm_precision { XALM_PRECISION_BF16 = 0, XALM_PRECISION_F32 = 1 };
 int xalm_cuda_create_json(const char* config_json, int device, int max_tokens, int precision, xalm_cuda_model** out);
-/* Model families linked into this build ("Llama", "Nabalix", ...). */
+/* Model families linked into this build ("Llama", "Nabalix", "Bolovik", ...). */
 int xalm_cuda_family_count(void);
 const char* xalm_cuda_family_name(int index);
 /* The sequence is over: what it holds in the K/V cache and the recurrent state is given back; the next call starts at

@@ -146,7 +146,7 @@ def device_count_or_zero() -> int:
 
 
 def families() -> list:
-    """Model families linked into the library ("Llama", "Nabalix", ...)."""
+    """Model families linked into the library ("Llama", "Nabalix", "Bolovik", ...)."""
     L = lib()
     return [L.xalm_cuda_family_name(i).decode() for i in range(L.xalm_cuda_family_count())]
 
